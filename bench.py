@@ -1,0 +1,349 @@
+#!/usr/bin/env python
+"""Benchmark of the MixedQLinear hot path on B200.
+
+One step = one pass of the four linear layers of a Llama-2 decoder layer (fused-N shapes: qkv,
+o, gate+up int4 with 256 fp16 outlier columns, down int8) over M tokens of seeded synthetic
+activations: activation quantizer + fused int GEMM / outlier GEMM / dequantize per layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens M] [--model 7b|70b] [--impl reference]
+
+Prints one JSON line (rank 0).  `value` is whole-job TOPS (2*M*N*K summed over the layers / time)
+with inputs resident in HBM; `e2e` is the same metric through MixedQLinear.forward with the
+activations copied from pinned host memory and the outputs copied back inside the timed region.
+N > 1 (torchrun): the layers are column-sharded over the ranks and the outputs all-gathered.
+`--impl reference` times the reference's torch fake-quant simulation of the same layers on the
+host cores (a port of it; the reference checkout is not needed at run time).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "MixedQLinear TOPS (Llama-2 linear shapes, fused quantize+GEMM+dequant)"
+CPU_SAMPLE_TOKENS = 256
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--model", choices=["7b", "70b"], default="7b")
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--engine", choices=["auto", "tcgen05", "mma_sync"], default="auto")
+    ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layers", default="", help="comma-separated subset of layer names")
+    return ap.parse_args()
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.lines = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------
+def cpu_fake_quant_baseline(shapes, tokens, steps, warmup, seed=0):
+    """The reference's torch fake-quant simulation (experiments/quant_sim.py ActQuantWrapper around
+    nn.Linear with RTN-quantized weights), ported in oracle/fakequant.py, timed on the host cores."""
+    from oracle import fakequant
+    from quik_b200 import workloads
+    torch.set_num_threads(os.cpu_count() or 1)
+    layers = []
+    ops = 0.0
+    for (name, K, N, bits) in shapes:
+        g = torch.Generator().manual_seed(seed)
+        x = torch.randn(tokens, K, generator=g)
+        fp_idx = torch.randperm(K, generator=g)[:workloads.FP_FEATURES]
+        x[:, fp_idx] *= 20
+        w = (0.02 * torch.randn(N, K, generator=g)).half()
+        standin = workloads.standin_act_scales(K, fp_idx)
+        layer = fakequant.FakeQuantLinear(w, standin, workloads.FP_FEATURES, bits)
+        # weight fake-quantization is a one-off preparation step; plain RTN keeps the set-up short
+        wi = w[:, layer.q_idx].float()
+        sc = fakequant.weight_rtn_params(wi, bits, clip=False)
+        w[:, layer.q_idx] = fakequant.weight_rtn_quantize(wi, sc, bits).half()
+        layer.weight = w
+        layers.append((layer, x.half()))
+        ops += 2.0 * tokens * N * K
+    times = []
+    with torch.no_grad():
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            for layer, x in layers:
+                layer(x)
+            dt = time.perf_counter() - t0
+            if i >= warmup:
+                times.append(dt)
+    mean = sum(times) / len(times)
+    return {"value": ops / mean / 1e12, "unit": "TOPS", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{tokens} of the workload's tokens per layer, all {len(shapes)} layers, "
+                      f"{steps} timed passes after {warmup} warm-up (oracle/fakequant.py on "
+                      f"{os.cpu_count()} host cores)", "ms_per_step": mean * 1e3}
+
+
+def run_reference_arm(args, shapes, config):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 20))
+    warm = max(1, min(args.warmup, 3))
+    base = cpu_fake_quant_baseline(shapes, CPU_SAMPLE_TOKENS, steps, warm)
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "TOPS", "n_gpus": args.gpus,
+            "steps": steps, "warmup": warm, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": config,
+            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": base["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+def main():
+    args = parse_args()
+    from quik_b200 import workloads
+    shapes = workloads.LLAMA2_7B if args.model == "7b" else workloads.LLAMA2_70B
+    if args.layers:
+        keep = set(args.layers.split(","))
+        shapes = [s for s in shapes if s[0] in keep]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": f"llama2-{args.model} linear shapes {[(s[0], s[1], s[2], 'int%d' % s[3]) for s in shapes]}, "
+                          f"M={args.tokens} tokens, fp_features={workloads.FP_FEATURES}, "
+                          f"weights N(0,0.02) RTN+clip per channel, activations N(0,1) with x20 outlier columns",
+              "tokens": args.tokens, "parallelism": f"tp{world} (output-column shards + all-gather)" if world > 1 else "single GPU",
+              "l2": "per-step working set (weights + activations + outputs of the four layers) exceeds the 126 MB L2"}
+    if args.impl == "reference":
+        run_reference_arm(args, shapes, config)
+        return
+
+    import torch.distributed as dist
+    from quik_b200 import _lib
+    from quik_b200.qlinear import MixedQLinear
+    from quik_b200.tp import ColumnParallelMixedQLinear, shard_range
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+    _lib.set_engine({"auto": _lib.ENGINE_AUTO, "tcgen05": _lib.ENGINE_TCGEN05, "mma_sync": _lib.ENGINE_MMA_SYNC}[args.engine])
+    _lib.set_tile_n(args.tile_n)
+
+    M = args.tokens
+    cases, layers = [], []
+    for (name, K, N, bits) in shapes:
+        sl = shard_range(N, world, rank) if world > 1 else None
+        c = workloads.make_layer(name, M, K, N, bits, seed=0, device=dev, n_slice=sl)
+        cases.append(c)
+        layers.append(ColumnParallelMixedQLinear(c.module) if world > 1 else c.module)
+        torch.cuda.empty_cache()
+    total_ops = sum(2.0 * M * N * K for (_, K, N, _) in shapes)          # whole job, all ranks
+    alg_bytes = sum(c.algorithmic_bytes for c in cases)
+
+    # ---- CUDA-event hook around the fused GEMM launch (roofline of the dominant kernel)
+    pool = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            for _ in range(len(shapes) * (args.steps + 1))]
+    used = []
+    state = {"on": False, "i": 0}
+
+    def hook(mod, begin):
+        if not state["on"]:
+            return
+        if begin:
+            pool[state["i"]][0].record()
+        else:
+            pool[state["i"]][1].record()
+            used.append((state["i"], mod))
+            state["i"] += 1
+
+    MixedQLinear.launch_hook = hook
+
+    def step():
+        outs = []
+        for c, layer in zip(cases, layers):
+            outs.append(layer(c.x.unsqueeze(0)))
+        return outs
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sync_all()
+    assert _lib.device_status() == 0, "a bounded device wait ran out during warm-up"
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    state["on"] = True
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    sync_all()
+    state["on"] = False
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = t.item()
+    ms_step = ms_total / args.steps
+    value = total_ops / (ms_step * 1e-3) / 1e12
+
+    # ---- dominant-kernel roofline (this rank's launches)
+    gemm_ms, gemm_ops, per_layer = 0.0, 0.0, {}
+    for i, mod in used:
+        dt = pool[i][0].elapsed_time(pool[i][1])
+        ops = 2.0 * M * mod.out_features * mod.in_features
+        gemm_ms += dt
+        gemm_ops += ops
+        key = f"{mod.in_features}->{mod.out_features} int{mod.bits}"
+        per_layer.setdefault(key, []).append(dt)
+    peaks = load_peaks()
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    achieved = gemm_ops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
+                "frac": achieved / int8_peak if int8_peak else None, "traffic": None,
+                "kernel": "gemm_tcgen05_kernel (fused int8 GEMM + fp16 outlier GEMM + dequantize)",
+                "peak_source": f"2 x bf16 dense GEMM peak of {peaks['source']} ({peaks['bf16_tflops']} TF/s burst); "
+                               f"int8 runs at twice the bf16 rate on this part; nominal dense int8 is 4500",
+                "frac_of_nominal_4500": achieved / 4500.0,
+                "per_layer_us": {k: 1e3 * sum(v) / len(v) for k, v in per_layer.items()},
+                "hbm_frac_whole_step": (alg_bytes / (ms_step * 1e-3) / 1e9) / peaks["hbm_gbs"]}
+
+    # ---- end to end through the public API with host buffers
+    e2e = None
+    if not args.no_e2e:
+        hx = [c.x.cpu().pin_memory() for c in cases]
+        dx = [torch.empty_like(c.x) for c in cases]
+        n_out = [(c.N * (world if world > 1 else 1)) for c in cases]
+        ho = [torch.empty((1, M, n), dtype=torch.float16).pin_memory() for n in n_out]
+        h2d = sum(t.numel() * t.element_size() for t in hx)
+        d2h = sum(t.numel() * t.element_size() for t in ho)
+
+        def e2e_step():
+            for i, layer in enumerate(layers):
+                dx[i].copy_(hx[i], non_blocking=True)
+                out = layer(dx[i].unsqueeze(0))
+                ho[i].copy_(out, non_blocking=True)
+
+        e_steps = max(3, min(args.steps, 10))
+        for _ in range(3):
+            e2e_step()
+        sync_all()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(e_steps):
+            e2e_step()
+        b.record()
+        sync_all()
+        ms = a.elapsed_time(b)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        e2e = {"value": total_ops / (ms / e_steps * 1e-3) / 1e12, "unit": "TOPS", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": ms / e_steps, "steps": e_steps}
+    assert _lib.device_status() == 0, "a bounded device wait ran out"
+
+    cpu_base = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_base = cpu_fake_quant_baseline(shapes, CPU_SAMPLE_TOKENS, 5, 1)
+        cpu_base = {k: cpu_base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": config, "roofline": roofline,
+                "cpu_baseline": cpu_base, "e2e": e2e, "gpu_launches": 2 * len(shapes) * args.steps, "clocks": clocks,
+                "frac_of_int8_peak_whole_step": value / int8_peak}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,172 @@
+/*
+ * quik_b200 -- C ABI of the B200 (sm_100a) implementation of QUIK's mixed-precision
+ * quantized linear layer.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the CUDA
+ * stream it is given (a cudaStream_t passed as void*; NULL = legacy default
+ * stream) on the calling thread's current device, never allocates or frees
+ * device memory, never synchronises, and returns QUIK_OK (0) or a negative
+ * error code (see quik_strerror).  Inputs are borrowed and never modified.
+ * Outputs are caller-allocated.  All matrices are dense row-major.
+ *
+ * Each declaration cites the interface of the reference project
+ * (IST-DASLab/QUIK, paths relative to its root) that it replaces.
+ */
+#ifndef QUIK_B200_H_
+#define QUIK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------ */
+#define QUIK_OK                 0
+#define QUIK_ERR_NULL          -1   /* a required pointer is NULL                               */
+#define QUIK_ERR_BITS          -2   /* "bits argument must be either 4 or 8" (asymmetric.cpp:20) */
+#define QUIK_ERR_SHAPE         -3   /* size / divisibility requirement violated                 */
+#define QUIK_ERR_ALIGN         -4   /* a pointer or row pitch is not 16-byte aligned            */
+#define QUIK_ERR_DTYPE         -5   /* dtype code is not QUIK_F16 / QUIK_BF16 (or unsupported)  */
+#define QUIK_ERR_CUDA          -6   /* a CUDA runtime / driver call failed (quik_last_cuda_error)*/
+#define QUIK_ERR_SCRATCH       -7   /* scratch buffer missing or too small                      */
+#define QUIK_ERR_UNSUPPORTED   -8   /* valid for the reference, outside this build's limits     */
+#define QUIK_ERR_DEVICE_WAIT   -9   /* a bounded on-device wait ran out (reported via status)   */
+
+/* ---- element types of floating tensors --------------------------------------------------- */
+#define QUIK_F16   0
+#define QUIK_BF16  1
+
+/* ---- integer-GEMM engines (quik_config_set(QUIK_CFG_GEMM_ENGINE, ...)) -------------------- */
+#define QUIK_CFG_GEMM_ENGINE   1
+#define QUIK_ENGINE_AUTO       0    /* tcgen05 + TMA + TMEM where the shape allows, else mma.sync */
+#define QUIK_ENGINE_TCGEN05    1
+#define QUIK_ENGINE_MMA_SYNC   2
+/* Output-tile width of the tcgen05 engine: 0 = chosen by shape, 128 or 256. */
+#define QUIK_CFG_TILE_N        2
+/* 1 (default): int8 layers with M <= QUIK_SMALL_M_MAX use the weight-streaming engine; 0: never. */
+#define QUIK_CFG_SMALL_M       3
+
+const char *quik_version(void);
+const char *quik_strerror(int status);
+/* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
+const char *quik_last_cuda_error(void);
+int quik_config_set(int key, int value);
+int quik_config_get(int key);
+/* Every on-device wait (mbarrier, flag) is bounded; a kernel whose wait ran out records it in a
+ * per-device status word and returns early.  This call synchronises the current device, returns
+ * QUIK_OK or QUIK_ERR_DEVICE_WAIT, and clears the word when `clear` is non-zero. */
+int quik_device_status(int clear);
+
+/* ==== asymmetric activation quantizer ======================================================
+ * Replaces quik.asymmetric.quantize (src/asymmetric/asymmetric.cpp:16-25, kernel
+ * src/asymmetric/asymmetric.cu:340-584).
+ *   src          [rows, cols]  fp16 / bf16 (dtype)
+ *   int_indices  [num_int]     int64 column ids that are quantized, in output order
+ *   fp_indices   [num_fp]      int64 column ids copied verbatim, in output order
+ *   dst          bits=4: uint8 [rows, num_int/2], element 2j of the gathered row in the low
+ *                nibble of byte j;  bits=8: int8 [rows, num_int]
+ *   meta         [2*rows] dtype, interleaved (scale, zero) per row
+ *   fp_x         [rows, num_fp] dtype
+ * Requires num_int + num_fp == cols, num_int even, bits in {4, 8}, cols <= 65536.
+ */
+int quik_asym_quantize(const void *src, int dtype, int rows, int cols,
+                       const int64_t *int_indices, int num_int,
+                       const int64_t *fp_indices, int num_fp, int bits,
+                       void *dst, void *meta, void *fp_x, void *stream);
+
+/* Same operator with 16-bit column ids (a layer converts its index buffers once) and a
+ * choice of code layout: wide != 0 stores one int8 per code for bits=4 as well
+ * (dst int8 [rows, num_int]), the operand layout of the tensor-core GEMM.
+ * No counterpart in the reference; used by the fused layer path (experiments/qlinear.py:114-117).
+ */
+int quik_asym_quantize_u16(const void *src, int dtype, int rows, int cols,
+                           const uint16_t *int_indices, int num_int,
+                           const uint16_t *fp_indices, int num_fp, int bits, int wide,
+                           void *dst, void *meta, void *fp_x, void *stream);
+
+/* quik.asymmetric.find_meta (src/asymmetric/asymmetric.cpp:40-44, asymmetric.cu:263-338):
+ * meta[2r] = T(fmaxf((max_r - min_r) / (2^bits - 1), 1e-6f)), meta[2r+1] = min_r. */
+int quik_asym_find_meta(const void *src, int dtype, int rows, int cols, int bits,
+                        void *meta, void *stream);
+
+/* quik.asymmetric.quantizeOld (src/asymmetric/asymmetric.cpp:8-14, asymmetric.cu:13-117):
+ * quantize an already gathered matrix with a given meta; dst as in quik_asym_quantize with
+ * ceil(cols/2) bytes per row for bits=4. */
+int quik_asym_quantize_old(const void *src, int dtype, const void *meta, int rows, int cols,
+                           int bits, void *dst, void *stream);
+
+/* quik.asymmetric.dequantize (src/asymmetric/asymmetric.cpp:27-38, asymmetric.cu:119-233):
+ * out[r,c] = T(float(x[r,c]) * (s_r * sc_c) + ((z_r + 2^(bits-1) * s_r) * wred_c + float(y[r,c])))
+ * in fp32 with one final rounding.  x int32 [rows, cols]; meta [2*rows]; scale_col [cols];
+ * w_reduced [cols]; y, out [rows, cols] of dtype. */
+int quik_asym_dequantize(const int32_t *x, const void *meta, const void *scale_col,
+                         const void *w_reduced, const void *y, void *out, int dtype,
+                         int rows, int cols, int bits, void *stream);
+
+/* ==== symmetric ops ========================================================================
+ * quik.symmetric.quantize (src/symmetric/symmetric.cpp:9-21, symmetric.cu:6-78), fp16 only:
+ * q = rn(src / scale[row]) without clamping; bits=4 packs two nibbles per byte. */
+int quik_sym_quantize(const void *src, const void *scale, int rows, int cols, int bits,
+                      void *dst, void *stream);
+/* quik.symmetric.dequantize (src/symmetric/symmetric.cpp:23-42, symmetric.cu:80-152), fp16:
+ * out = hmul(hmul(half(x), scale_row[r]), scale_col[c]) + y; x_bits 8 (int8), 16 (fp16), 32 (int32). */
+int quik_sym_dequantize(const void *x, int x_bits, const void *scale_row, const void *scale_col,
+                        const void *y, void *out, int rows, int cols, void *stream);
+
+/* ==== integer GEMM =========================================================================
+ * quik.matmul.int8Matmul (src/matmul/matmul.cpp:43-48, matmul.cu:98-136):
+ * C[m,n] = sum_k A[m,k] * B[n,k], int8 x int8 -> exact int32.  A [M,K], B [N,K], C [M,N].
+ * Requires K % 16 == 0 and 16-byte aligned A, B. */
+int quik_int8_matmul(const int8_t *A, const int8_t *B, int32_t *C, int M, int N, int K,
+                     void *stream);
+
+/* quik.matmul.int4Matmul (src/matmul/matmul.cpp:8-13, matmul.cu:17-55): the same contraction on
+ * packed int4 operands, A uint8 [M,K/2], B uint8 [N,K/2] (K counts int4 elements, K % 32 == 0).
+ * The operands are widened to int8 in `scratch` (device memory, at least
+ * quik_int4_matmul_scratch_bytes(M,N,K) bytes, 256-byte aligned) and fed to the int8 engine. */
+size_t quik_int4_matmul_scratch_bytes(int M, int N, int K);
+int quik_int4_matmul(const uint8_t *A, const uint8_t *B, int32_t *C, int M, int N, int K,
+                     void *scratch, size_t scratch_bytes, void *stream);
+
+/* Widen packed int4 [rows, cols/2] to int8 [rows, cols] (layout rule of include/int4.h:78-98). */
+int quik_unpack_int4(const uint8_t *src, int8_t *dst, int rows, int cols, void *stream);
+
+/* ==== fused GEMM + dequantize ==============================================================
+ * quik.asymmetric.int4FusedDequantize / int8FusedDequantize
+ * (src/asymmetric/asymmetric.cpp:46-88, src/asymmetric/fused_dequantize.cu:9-119) and, with
+ * zero_row = w_reduced = NULL, quik.symmetric.int4FusedDequantize / int8FusedDequantize
+ * (src/symmetric/symmetric.cpp:44-70, src/symmetric/fused_dequantize.cu:9-107):
+ *   out = half(acc * scale_row * scale_col + (zero_row + shift_value * scale_row) * w_reduced + y)
+ * evaluated in fp32 with one final rounding (the reference rounds every operation to fp16).
+ * A, B: int8 [M,K] / [N,K] when bits == 8; packed int4 when bits == 4 (then scratch as for
+ * quik_int4_matmul).  scale_row, zero_row [M]; scale_col, w_reduced [N]; y, out [M,N]; fp16. */
+int quik_fused_dequantize(const void *A, const void *B, int bits,
+                          const void *scale_row, const void *scale_col, float shift_value,
+                          const void *zero_row, const void *w_reduced, const void *y, void *out,
+                          int M, int N, int K, void *scratch, size_t scratch_bytes, void *stream);
+
+/* ==== the fused layer ======================================================================
+ * Replaces the body of MixedQLinear.forward after the quantizer (experiments/qlinear.py:122-145:
+ * F.linear on the outlier columns, int4Matmul / int8Matmul, asymmetric.dequantize) by one launch:
+ *   out[m,n] = T( float(sum_k q[m,k] * w[n,k]) * (s_m * sw_n)
+ *                 + ((z_m + 2^(bits-1) * s_m) * wred_n + sum_j fp_x[m,j] * fp_w[n,j] + bias_n) )
+ *   q        int8 [M, K_int]  activation codes, one per byte (quik_asym_quantize_u16 wide=1), or,
+ *            when q_packed != 0, the reference layout (uint8 [M, K_int/2] for bits=4)
+ *   w        int8 [N, K_int]  weight codes, one per byte; or packed when w_packed != 0
+ *   meta     [2*M] dtype (scale, zero) per row;  scale_col, w_reduced [N] dtype
+ *   fp_x     [M, F] dtype, fp_w [N, F] dtype (F may be 0: both NULL);  bias [N] dtype or NULL
+ *   out      [M, N] dtype
+ * Packed operands are accepted by the weight-streaming engine (M <= QUIK_SMALL_M_MAX);
+ * one-code-per-byte operands by the tensor-core engine.  K_int % 16 == 0, F % 8 == 0. */
+#define QUIK_SMALL_M_MAX 16
+int quik_mixed_linear(const void *q, int q_packed, const void *w, int w_packed,
+                      const void *meta, const void *scale_col, const void *w_reduced,
+                      const void *fp_x, const void *fp_w, const void *bias, void *out,
+                      int dtype, int M, int N, int K_int, int F, int bits, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QUIK_B200_H_ */

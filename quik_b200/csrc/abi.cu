@@ -1,0 +1,294 @@
+// extern "C" entry points of libquik_b200: argument validation and dispatch to the kernels.
+// The checks mirror the reference's TORCH_CHECKs (QUIK src/asymmetric/asymmetric.cpp:16-44,
+// src/asymmetric/asymmetric.cu:185-196,519-524, src/matmul/matmul.cpp:8-48) as status codes.
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace quik {
+namespace {
+thread_local char g_err[256] = "";
+int g_engine = QUIK_ENGINE_AUTO;
+int g_small_m = 1;
+}  // namespace
+
+void set_cuda_error(cudaError_t e, const char *where) {
+  snprintf(g_err, sizeof(g_err), "%s: %s", where, cudaGetErrorString(e));
+}
+
+int num_sms() {
+  static int cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+static bool dtype_ok(int dtype) { return dtype == QUIK_F16 || dtype == QUIK_BF16; }
+
+static int run_int8_gemm(const int8_t *A, const int8_t *B, int M, int N, int K, const Epilogue &ep,
+                         cudaStream_t st) {
+  if (g_engine == QUIK_ENGINE_MMA_SYNC) return launch_gemm_mma_sync(A, B, M, N, K, ep, st);
+  return launch_gemm_tcgen05(A, B, M, N, K, ep, st);
+}
+
+}  // namespace quik
+
+using namespace quik;
+
+extern "C" {
+
+const char *quik_version(void) { return "quik_b200 0.1 (sm_100a)"; }
+
+const char *quik_strerror(int status) {
+  switch (status) {
+    case QUIK_OK: return "ok";
+    case QUIK_ERR_NULL: return "a required pointer is NULL";
+    case QUIK_ERR_BITS: return "bits argument must be either 4 or 8";
+    case QUIK_ERR_SHAPE: return "invalid sizes (column counts must add up, integer columns even / multiple of 16 or 32)";
+    case QUIK_ERR_ALIGN: return "pointer or row pitch is not 16-byte aligned";
+    case QUIK_ERR_DTYPE: return "unsupported element type";
+    case QUIK_ERR_CUDA: return "CUDA call failed";
+    case QUIK_ERR_SCRATCH: return "scratch buffer missing or too small";
+    case QUIK_ERR_UNSUPPORTED: return "configuration not supported by this build";
+    case QUIK_ERR_DEVICE_WAIT: return "a bounded on-device wait ran out";
+    default: return "unknown status";
+  }
+}
+
+const char *quik_last_cuda_error(void) { return g_err; }
+
+int quik_config_set(int key, int value) {
+  if (key == QUIK_CFG_GEMM_ENGINE) {
+    if (value < QUIK_ENGINE_AUTO || value > QUIK_ENGINE_MMA_SYNC) return QUIK_ERR_UNSUPPORTED;
+    g_engine = value;
+    return QUIK_OK;
+  }
+  if (key == QUIK_CFG_TILE_N) {
+    if (value != 0 && value != 128 && value != 256) return QUIK_ERR_UNSUPPORTED;
+    set_tile_n(value);
+    return QUIK_OK;
+  }
+  if (key == QUIK_CFG_SMALL_M) {
+    g_small_m = value ? 1 : 0;
+    return QUIK_OK;
+  }
+  return QUIK_ERR_UNSUPPORTED;
+}
+
+int quik_config_get(int key) {
+  if (key == QUIK_CFG_SMALL_M) return g_small_m;
+  if (key == QUIK_CFG_GEMM_ENGINE) return g_engine;
+  if (key == QUIK_CFG_TILE_N) return get_tile_n();
+  return QUIK_ERR_UNSUPPORTED;
+}
+
+int quik_device_status(int clear) { return device_status_read(clear); }
+
+static int check_quantize_args(const void *src, int dtype, int rows, int cols, const void *int_idx, int num_int,
+                               const void *fp_idx, int num_fp, int bits, void *dst, void *meta, void *fp_x) {
+  if (bits != 4 && bits != 8) return QUIK_ERR_BITS;
+  if (!dtype_ok(dtype)) return QUIK_ERR_DTYPE;
+  if (rows < 0 || cols <= 0 || num_int <= 0 || num_fp < 0) return QUIK_ERR_SHAPE;
+  if (num_int + num_fp != cols) return QUIK_ERR_SHAPE;   // asymmetric.cu:519-521
+  if (num_int % 2 != 0) return QUIK_ERR_SHAPE;           // asymmetric.cu:522-524
+  if (cols > 65536) return QUIK_ERR_UNSUPPORTED;
+  if (rows == 0) return QUIK_OK;
+  if (!src || !int_idx || !dst || !meta) return QUIK_ERR_NULL;
+  if (num_fp > 0 && (!fp_idx || !fp_x)) return QUIK_ERR_NULL;
+  return QUIK_OK;
+}
+
+int quik_asym_quantize(const void *src, int dtype, int rows, int cols, const int64_t *int_indices, int num_int,
+                       const int64_t *fp_indices, int num_fp, int bits, void *dst, void *meta, void *fp_x,
+                       void *stream) {
+  int rc = check_quantize_args(src, dtype, rows, cols, int_indices, num_int, fp_indices, num_fp, bits, dst, meta, fp_x);
+  if (rc != QUIK_OK) return rc;
+  return launch_asym_quantize(src, dtype, rows, cols, int_indices, num_int, fp_indices, num_fp, 8, bits, 0, dst,
+                              meta, fp_x, static_cast<cudaStream_t>(stream));
+}
+
+int quik_asym_quantize_u16(const void *src, int dtype, int rows, int cols, const uint16_t *int_indices, int num_int,
+                           const uint16_t *fp_indices, int num_fp, int bits, int wide, void *dst, void *meta,
+                           void *fp_x, void *stream) {
+  int rc = check_quantize_args(src, dtype, rows, cols, int_indices, num_int, fp_indices, num_fp, bits, dst, meta, fp_x);
+  if (rc != QUIK_OK) return rc;
+  return launch_asym_quantize(src, dtype, rows, cols, int_indices, num_int, fp_indices, num_fp, 2, bits, wide, dst,
+                              meta, fp_x, static_cast<cudaStream_t>(stream));
+}
+
+int quik_asym_find_meta(const void *src, int dtype, int rows, int cols, int bits, void *meta, void *stream) {
+  if (bits != 4 && bits != 8) return QUIK_ERR_BITS;
+  if (!dtype_ok(dtype)) return QUIK_ERR_DTYPE;
+  if (rows < 0 || cols <= 0) return QUIK_ERR_SHAPE;
+  if (rows == 0) return QUIK_OK;
+  if (!src || !meta) return QUIK_ERR_NULL;
+  return launch_find_meta(src, dtype, rows, cols, bits, meta, static_cast<cudaStream_t>(stream));
+}
+
+int quik_asym_quantize_old(const void *src, int dtype, const void *meta, int rows, int cols, int bits, void *dst,
+                           void *stream) {
+  if (bits != 4 && bits != 8) return QUIK_ERR_BITS;
+  if (!dtype_ok(dtype)) return QUIK_ERR_DTYPE;
+  if (rows < 0 || cols < 0) return QUIK_ERR_SHAPE;
+  if (rows == 0 || cols == 0) return QUIK_OK;
+  if (!src || !meta || !dst) return QUIK_ERR_NULL;
+  return launch_quantize_old(src, dtype, meta, rows, cols, bits, dst, static_cast<cudaStream_t>(stream));
+}
+
+int quik_asym_dequantize(const int32_t *x, const void *meta, const void *scale_col, const void *w_reduced,
+                         const void *y, void *out, int dtype, int rows, int cols, int bits, void *stream) {
+  if (bits != 4 && bits != 8) return QUIK_ERR_BITS;
+  if (!dtype_ok(dtype)) return QUIK_ERR_DTYPE;
+  if (rows < 0 || cols < 0) return QUIK_ERR_SHAPE;
+  if (rows == 0 || cols == 0) return QUIK_OK;
+  if (!x || !meta || !scale_col || !w_reduced || !y || !out) return QUIK_ERR_NULL;
+  return launch_asym_dequantize(x, meta, scale_col, w_reduced, y, out, dtype, rows, cols, bits,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int quik_sym_quantize(const void *src, const void *scale, int rows, int cols, int bits, void *dst, void *stream) {
+  if (bits != 4 && bits != 8) return QUIK_ERR_BITS;
+  if (rows < 0 || cols < 0) return QUIK_ERR_SHAPE;
+  if (rows == 0 || cols == 0) return QUIK_OK;
+  if (!src || !scale || !dst) return QUIK_ERR_NULL;
+  return launch_sym_quantize(src, scale, rows, cols, bits, dst, static_cast<cudaStream_t>(stream));
+}
+
+int quik_sym_dequantize(const void *x, int x_bits, const void *scale_row, const void *scale_col, const void *y,
+                        void *out, int rows, int cols, void *stream) {
+  if (x_bits != 8 && x_bits != 16 && x_bits != 32) return QUIK_ERR_BITS;
+  if (rows < 0 || cols < 0) return QUIK_ERR_SHAPE;
+  if (rows == 0 || cols == 0) return QUIK_OK;
+  if (!x || !scale_row || !scale_col || !y || !out) return QUIK_ERR_NULL;
+  return launch_sym_dequantize(x, x_bits, scale_row, scale_col, y, out, rows, cols,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int quik_int8_matmul(const int8_t *A, const int8_t *B, int32_t *C, int M, int N, int K, void *stream) {
+  if (M < 0 || N < 0 || K <= 0 || K % 16 != 0) return QUIK_ERR_SHAPE;
+  if (M == 0 || N == 0) return QUIK_OK;
+  if (!A || !B || !C) return QUIK_ERR_NULL;
+  if (!aligned16(A) || !aligned16(B)) return QUIK_ERR_ALIGN;
+  Epilogue ep{};
+  ep.mode = 0;
+  ep.C = C;
+  return run_int8_gemm(A, B, M, N, K, ep, static_cast<cudaStream_t>(stream));
+}
+
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+size_t quik_int4_matmul_scratch_bytes(int M, int N, int K) {
+  if (M < 0 || N < 0 || K < 0) return 0;
+  return align256((size_t)M * K) + align256((size_t)N * K);
+}
+
+int quik_unpack_int4(const uint8_t *src, int8_t *dst, int rows, int cols, void *stream) {
+  if (rows < 0 || cols < 0 || cols % 2 != 0) return QUIK_ERR_SHAPE;
+  if (rows == 0 || cols == 0) return QUIK_OK;
+  if (!src || !dst) return QUIK_ERR_NULL;
+  return launch_unpack_int4(src, dst, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+static int widen_operands(const uint8_t *A, const uint8_t *B, int M, int N, int K, void *scratch,
+                          size_t scratch_bytes, cudaStream_t st, const int8_t **A8, const int8_t **B8) {
+  if (!scratch || scratch_bytes < quik_int4_matmul_scratch_bytes(M, N, K)) return QUIK_ERR_SCRATCH;
+  if ((reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) return QUIK_ERR_ALIGN;
+  int8_t *a8 = static_cast<int8_t *>(scratch);
+  int8_t *b8 = a8 + align256((size_t)M * K);
+  int rc = launch_unpack_int4(A, a8, M, K, st);
+  if (rc != QUIK_OK) return rc;
+  rc = launch_unpack_int4(B, b8, N, K, st);
+  if (rc != QUIK_OK) return rc;
+  *A8 = a8;
+  *B8 = b8;
+  return QUIK_OK;
+}
+
+int quik_int4_matmul(const uint8_t *A, const uint8_t *B, int32_t *C, int M, int N, int K, void *scratch,
+                     size_t scratch_bytes, void *stream) {
+  if (M < 0 || N < 0 || K <= 0 || K % 32 != 0) return QUIK_ERR_SHAPE;
+  if (M == 0 || N == 0) return QUIK_OK;
+  if (!A || !B || !C) return QUIK_ERR_NULL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int8_t *a8, *b8;
+  int rc = widen_operands(A, B, M, N, K, scratch, scratch_bytes, st, &a8, &b8);
+  if (rc != QUIK_OK) return rc;
+  Epilogue ep{};
+  ep.mode = 0;
+  ep.C = C;
+  return run_int8_gemm(a8, b8, M, N, K, ep, st);
+}
+
+int quik_fused_dequantize(const void *A, const void *B, int bits, const void *scale_row, const void *scale_col,
+                          float shift_value, const void *zero_row, const void *w_reduced, const void *y, void *out,
+                          int M, int N, int K, void *scratch, size_t scratch_bytes, void *stream) {
+  if (bits != 4 && bits != 8) return QUIK_ERR_BITS;
+  if (M < 0 || N < 0 || K <= 0 || K % (bits == 4 ? 32 : 16) != 0) return QUIK_ERR_SHAPE;
+  if (M == 0 || N == 0) return QUIK_OK;
+  if (!A || !B || !scale_row || !scale_col || !y || !out) return QUIK_ERR_NULL;
+  if ((zero_row == nullptr) != (w_reduced == nullptr)) return QUIK_ERR_NULL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int8_t *a8 = static_cast<const int8_t *>(A), *b8 = static_cast<const int8_t *>(B);
+  if (bits == 4) {
+    int rc = widen_operands(static_cast<const uint8_t *>(A), static_cast<const uint8_t *>(B), M, N, K, scratch,
+                            scratch_bytes, st, &a8, &b8);
+    if (rc != QUIK_OK) return rc;
+  } else if (!aligned16(A) || !aligned16(B)) {
+    return QUIK_ERR_ALIGN;
+  }
+  Epilogue ep{};
+  ep.mode = 1;
+  ep.dtype = QUIK_F16;
+  ep.out = out;
+  ep.scale_row = scale_row;
+  ep.zero_row = zero_row;
+  ep.scale_col = scale_col;
+  ep.w_reduced = w_reduced;
+  ep.y = y;
+  ep.shift_value = shift_value;
+  return run_int8_gemm(a8, b8, M, N, K, ep, st);
+}
+
+int quik_mixed_linear(const void *q, int q_packed, const void *w, int w_packed, const void *meta,
+                      const void *scale_col, const void *w_reduced, const void *fp_x, const void *fp_w,
+                      const void *bias, void *out, int dtype, int M, int N, int K_int, int F, int bits,
+                      void *stream) {
+  if (bits != 4 && bits != 8) return QUIK_ERR_BITS;
+  if (!dtype_ok(dtype)) return QUIK_ERR_DTYPE;
+  if (M < 0 || N < 0 || K_int <= 0 || F < 0 || K_int % 16 != 0 || F % 8 != 0) return QUIK_ERR_SHAPE;
+  if (M == 0 || N == 0) return QUIK_OK;
+  if (!q || !w || !meta || !scale_col || !w_reduced || !out) return QUIK_ERR_NULL;
+  if (F > 0 && (!fp_x || !fp_w)) return QUIK_ERR_NULL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Epilogue ep{};
+  ep.mode = 1;
+  ep.dtype = dtype;
+  ep.out = out;
+  ep.meta = meta;
+  ep.scale_col = scale_col;
+  ep.w_reduced = w_reduced;
+  ep.bias = bias;
+  ep.shift_value = bits == 4 ? 8.0f : 128.0f;
+  ep.fp_a = F > 0 ? fp_x : nullptr;
+  ep.fp_b = F > 0 ? fp_w : nullptr;
+  ep.F = F;
+  const bool packed4 = bits == 4 && (q_packed || w_packed);
+  if (packed4) {
+    // packed int4 operands: weight-streaming engine; both operands must be packed
+    if (!(q_packed && w_packed)) return QUIK_ERR_UNSUPPORTED;
+    if (K_int % 32 != 0) return QUIK_ERR_SHAPE;
+    return launch_small_m(q, w, 4, M, N, K_int, ep, st);
+  }
+  // one code per byte: int8 layers with few tokens also stream their weights
+  if (bits == 8 && M <= QUIK_SMALL_M_MAX && g_small_m != 0)
+    return launch_small_m(q, w, 8, M, N, K_int, ep, st);
+  return run_int8_gemm(static_cast<const int8_t *>(q), static_cast<const int8_t *>(w), M, N, K_int, ep, st);
+}
+
+}  // extern "C"

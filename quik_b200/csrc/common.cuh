@@ -1,0 +1,110 @@
+// Shared helpers for the quik_b200 CUDA sources: status codes, dtype traits, launch checks.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/quik_b200.h"
+
+namespace quik {
+
+// ---- host-side error plumbing -------------------------------------------------------------
+void set_cuda_error(cudaError_t e, const char *where);   // abi.cu
+int num_sms();                                           // abi.cu (cached per device)
+
+#define QUIK_CUDA_TRY(expr)                                        \
+  do {                                                             \
+    cudaError_t _e = (expr);                                       \
+    if (_e != cudaSuccess) {                                       \
+      ::quik::set_cuda_error(_e, #expr);                           \
+      return QUIK_ERR_CUDA;                                        \
+    }                                                              \
+  } while (0)
+
+inline int check_launch(const char *what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_cuda_error(e, what);
+    return QUIK_ERR_CUDA;
+  }
+  return QUIK_OK;
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- device status word (bounded waits report here); lives in gemm_tcgen05.cu ---------------
+int device_status_read(int clear);   // synchronises the device
+void set_tile_n(int n);               // 0 = by shape, 128 or 256
+int get_tile_n();
+
+// ---- dtype traits ---------------------------------------------------------------------------
+template <typename T> struct Traits;
+template <> struct Traits<__half> {
+  using T2 = __half2;
+  static __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_float(float v) { return __float2half(v); }
+  static __device__ __forceinline__ int to_int_rn(__half v) { return __half2int_rn(v); }
+};
+template <> struct Traits<__nv_bfloat16> {
+  using T2 = __nv_bfloat162;
+  static __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ int to_int_rn(__nv_bfloat16 v) { return __bfloat162int_rn(v); }
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---- launchers implemented in the individual .cu files ---------------------------------------
+int launch_asym_quantize(const void *src, int dtype, int rows, int cols, const void *int_idx,
+                         int num_int, const void *fp_idx, int num_fp, int idx_bytes, int bits,
+                         int wide, void *dst, void *meta, void *fp_x, cudaStream_t st);
+int launch_find_meta(const void *src, int dtype, int rows, int cols, int bits, void *meta,
+                     cudaStream_t st);
+int launch_quantize_old(const void *src, int dtype, const void *meta, int rows, int cols, int bits,
+                        void *dst, cudaStream_t st);
+int launch_sym_quantize(const void *src, const void *scale, int rows, int cols, int bits, void *dst,
+                        cudaStream_t st);
+int launch_asym_dequantize(const int32_t *x, const void *meta, const void *scale_col,
+                           const void *w_reduced, const void *y, void *out, int dtype, int rows,
+                           int cols, int bits, cudaStream_t st);
+int launch_sym_dequantize(const void *x, int x_bits, const void *scale_row, const void *scale_col,
+                          const void *y, void *out, int rows, int cols, cudaStream_t st);
+int launch_unpack_int4(const uint8_t *src, int8_t *dst, int rows, int cols, cudaStream_t st);
+
+// Epilogue description shared by the GEMM engines.
+struct Epilogue {
+  int mode;                 // 0: int32 C; 1: dequantize to `out`
+  int dtype;                // QUIK_F16 / QUIK_BF16 of every floating operand
+  int32_t *C;               // mode 0
+  void *out;                // mode 1, [M, N]
+  const void *meta;         // interleaved (scale, zero) per row, or NULL when scale_row is given
+  const void *scale_row;    // [M] (fused-op form) or NULL
+  const void *zero_row;     // [M] or NULL (symmetric)
+  const void *scale_col;    // [N]
+  const void *w_reduced;    // [N] or NULL (symmetric)
+  const void *bias;         // [N] or NULL
+  const void *y;            // [M, N] addend or NULL
+  float shift_value;        // 8 / 128 or caller-given
+  const void *fp_a;         // [M, F] outlier activations or NULL
+  const void *fp_b;         // [N, F] outlier weights or NULL
+  int F;
+};
+
+int launch_gemm_tcgen05(const int8_t *A, const int8_t *B, int M, int N, int K, const Epilogue &ep,
+                        cudaStream_t st);
+int launch_gemm_mma_sync(const int8_t *A, const int8_t *B, int M, int N, int K, const Epilogue &ep,
+                         cudaStream_t st);
+int launch_small_m(const void *q, const void *w, int bits, int M, int N, int K_int,
+                   const Epilogue &ep, cudaStream_t st);
+
+}  // namespace quik

@@ -1,0 +1,337 @@
+// Activation quantizers.
+//
+// asym_quantize_kernel: per-token asymmetric int4/int8 quantizer with outlier-column gather.
+// Semantics follow the reference kernel (QUIK src/asymmetric/asymmetric.cu:340-490): per row,
+// max/min over the gathered integer columns, scale = T(fmaxf((max-min)/(2^b-1), 1e-6f)), zero =
+// min, code = clamp(rn(hdiv(hsub(x, zero), scale)), 0, 2^b-1) - 2^(b-1), outlier columns copied.
+//
+// Design for B200: the reference reads every row three times through 8-byte indices with 2-byte
+// loads and one 1024-thread block per row.  Here a CTA keeps the column ids in shared memory as
+// 16-bit values for its whole lifetime, streams each row from HBM exactly once with 128-bit
+// loads into shared memory, and does min/max (warp shuffles), quantize+pack and the outlier
+// gather from that copy.  HBM traffic per row: cols*2 bytes in, codes + outliers + meta out.
+#include "common.cuh"
+
+namespace quik {
+
+namespace {
+
+constexpr int kQuantThreads = 256;
+
+template <typename T> __device__ __forceinline__ T t_sub(T a, T b) { return __hsub(a, b); }
+template <typename T> __device__ __forceinline__ T t_div(T a, T b) { return __hdiv(a, b); }
+
+template <typename T, int BITS>
+__device__ __forceinline__ int quantize_code(T x, T zero, T scale) {
+  constexpr int kMaxQ = (1 << BITS) - 1;
+  constexpr int kShift = 1 << (BITS - 1);
+  int v = Traits<T>::to_int_rn(t_div(t_sub(x, zero), scale));
+  return min(max(v, 0), kMaxQ) - kShift;
+}
+
+// Block-wide max/min of per-thread partials; every thread receives the result.
+__device__ __forceinline__ void block_minmax(float &mx, float &mn, float *red /* [2*warps] */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  mx = warp_max(mx);
+  mn = warp_min(mn);
+  if (lane == 0) {
+    red[warp] = mx;
+    red[nwarps + warp] = mn;
+  }
+  __syncthreads();
+  mx = red[0];
+  mn = red[nwarps];
+  for (int w = 1; w < nwarps; ++w) {
+    mx = fmaxf(mx, red[w]);
+    mn = fminf(mn, red[nwarps + w]);
+  }
+  __syncthreads();
+}
+
+// IdxT: int64_t (reference ABI) or uint16_t (layer-cached ids).
+template <typename T, int BITS, bool WIDE, typename IdxT>
+__global__ void __launch_bounds__(kQuantThreads)
+asym_quantize_kernel(const T *__restrict__ src, const IdxT *__restrict__ int_idx,
+                     const IdxT *__restrict__ fp_idx, int rows, int cols, int num_int, int num_fp,
+                     uint8_t *__restrict__ dst, T *__restrict__ meta, T *__restrict__ fp_x,
+                     int vec_load, int vec_store) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int num_chunks = (num_int + 7) >> 3;           // 8 codes per chunk
+  const int int_pad = num_chunks << 3;
+  uint16_t *s_int = reinterpret_cast<uint16_t *>(smem_raw);               // [int_pad]
+  uint16_t *s_fp = s_int + int_pad;                                       // [num_fp rounded to 8]
+  const int fp_pad = (num_fp + 7) & ~7;
+  T *s_row = reinterpret_cast<T *>(s_fp + fp_pad);                        // [cols rounded to 8]
+  const int cols_pad = (cols + 7) & ~7;
+  float *s_red = reinterpret_cast<float *>(s_row + cols_pad);             // [2 * warps]
+
+  const int tid = threadIdx.x;
+  // column ids -> shared memory, once per CTA; the pad of the last chunk repeats the first id so
+  // that it never changes the row's max/min.
+  for (int i = tid; i < int_pad; i += kQuantThreads)
+    s_int[i] = static_cast<uint16_t>(i < num_int ? int_idx[i] : int_idx[0]);
+  for (int i = tid; i < num_fp; i += kQuantThreads) s_fp[i] = static_cast<uint16_t>(fp_idx[i]);
+
+  constexpr int kBytesPerChunk = (BITS == 4 && !WIDE) ? 4 : 8;
+  const size_t dst_pitch = (BITS == 4 && !WIDE) ? (size_t)(num_int >> 1) : (size_t)num_int;
+
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T *row = src + (size_t)r * cols;
+    __syncthreads();   // previous row fully consumed (and ids visible on the first trip)
+    if (vec_load) {
+      const uint4 *g = reinterpret_cast<const uint4 *>(row);
+      uint4 *s = reinterpret_cast<uint4 *>(s_row);
+      for (int i = tid; i < (cols >> 3); i += kQuantThreads) s[i] = __ldg(g + i);
+    } else {
+      for (int i = tid; i < cols; i += kQuantThreads) s_row[i] = row[i];
+    }
+    __syncthreads();
+
+    // ---- pass 1: max / min over the gathered integer columns
+    float mx = -INFINITY, mn = INFINITY;
+    for (int c = tid; c < num_chunks; c += kQuantThreads) {
+      const uint4 idv = *reinterpret_cast<const uint4 *>(s_int + (c << 3));
+      const uint32_t w[4] = {idv.x, idv.y, idv.z, idv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = Traits<T>::to_float(s_row[w[j] & 0xffffu]);
+        const float b = Traits<T>::to_float(s_row[w[j] >> 16]);
+        mx = fmaxf(mx, fmaxf(a, b));
+        mn = fminf(mn, fminf(a, b));
+      }
+    }
+    block_minmax(mx, mn, s_red);
+    const T scale = Traits<T>::from_float(fmaxf((mx - mn) / (float)((1 << BITS) - 1), 1e-6f));
+    const T zero = Traits<T>::from_float(mn);           // exact: mn is a value of type T
+    if (tid == 0) {
+      meta[2 * (size_t)r] = scale;
+      meta[2 * (size_t)r + 1] = zero;
+    }
+
+    // ---- pass 2: quantize + pack
+    uint8_t *drow = dst + (size_t)r * dst_pitch;
+    for (int c = tid; c < num_chunks; c += kQuantThreads) {
+      const uint4 idv = *reinterpret_cast<const uint4 *>(s_int + (c << 3));
+      const uint32_t w[4] = {idv.x, idv.y, idv.z, idv.w};
+      int v[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[2 * j] = quantize_code<T, BITS>(s_row[w[j] & 0xffffu], zero, scale);
+        v[2 * j + 1] = quantize_code<T, BITS>(s_row[w[j] >> 16], zero, scale);
+      }
+      if (BITS == 4 && !WIDE) {
+        uint32_t p = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) p |= (uint32_t)(v[j] & 0xF) << (4 * j);
+        if (vec_store) {
+          *reinterpret_cast<uint32_t *>(drow + (size_t)c * 4) = p;
+        } else {
+          const int nbytes = min(4, (num_int >> 1) - c * 4);
+          for (int j = 0; j < nbytes; ++j) drow[c * 4 + j] = (uint8_t)(p >> (8 * j));
+        }
+      } else {
+        uint2 p;
+        p.x = (uint32_t)(v[0] & 0xFF) | ((uint32_t)(v[1] & 0xFF) << 8) |
+              ((uint32_t)(v[2] & 0xFF) << 16) | ((uint32_t)(v[3] & 0xFF) << 24);
+        p.y = (uint32_t)(v[4] & 0xFF) | ((uint32_t)(v[5] & 0xFF) << 8) |
+              ((uint32_t)(v[6] & 0xFF) << 16) | ((uint32_t)(v[7] & 0xFF) << 24);
+        if (vec_store) {
+          *reinterpret_cast<uint2 *>(drow + (size_t)c * 8) = p;
+        } else {
+          const int nbytes = min(8, num_int - c * 8);
+          for (int j = 0; j < nbytes; ++j)
+            drow[c * 8 + j] = (uint8_t)((j < 4 ? p.x >> (8 * j) : p.y >> (8 * (j - 4))) & 0xFF);
+        }
+      }
+    }
+    (void)kBytesPerChunk;
+
+    // ---- outlier columns, verbatim
+    T *frow = fp_x + (size_t)r * num_fp;
+    for (int j = tid; j < num_fp; j += kQuantThreads) frow[j] = s_row[s_fp[j]];
+  }
+}
+
+template <typename T, int BITS, bool WIDE, typename IdxT>
+int launch_asym_t(const void *src, int rows, int cols, const void *int_idx, int num_int,
+                  const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x,
+                  cudaStream_t st) {
+  const int int_pad = ((num_int + 7) >> 3) << 3, fp_pad = (num_fp + 7) & ~7,
+            cols_pad = (cols + 7) & ~7;
+  const size_t smem = (size_t)(int_pad + fp_pad) * 2 + (size_t)cols_pad * sizeof(T) +
+                      2 * (kQuantThreads / 32) * sizeof(float);
+  auto kern = asym_quantize_kernel<T, BITS, WIDE, IdxT>;
+  if (smem > 48 * 1024)
+    QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int per_sm = 1;
+  QUIK_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kQuantThreads, smem));
+  if (per_sm < 1) return QUIK_ERR_UNSUPPORTED;
+  // A few CTAs per SM hide the load latency; more would only repeat the id staging.
+  const int grid = max(1, min(rows, num_sms() * min(per_sm, 4)));
+  const int vec_load = (cols % 8 == 0) && aligned16(src);
+  const bool packed = (BITS == 4 && !WIDE);
+  const int vec_store = (num_int % 8 == 0) &&
+                        ((reinterpret_cast<uintptr_t>(dst) & (packed ? 3u : 7u)) == 0);
+  kern<<<grid, kQuantThreads, smem, st>>>(
+      static_cast<const T *>(src), static_cast<const IdxT *>(int_idx),
+      static_cast<const IdxT *>(fp_idx), rows, cols, num_int, num_fp, static_cast<uint8_t *>(dst),
+      static_cast<T *>(meta), static_cast<T *>(fp_x), vec_load, vec_store);
+  return check_launch("asym_quantize_kernel");
+}
+
+template <typename T, typename IdxT>
+int dispatch_bits(int bits, int wide, const void *src, int rows, int cols, const void *int_idx,
+                  int num_int, const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x,
+                  cudaStream_t st) {
+  if (bits == 8)
+    return launch_asym_t<T, 8, true, IdxT>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
+                                           meta, fp_x, st);
+  if (wide)
+    return launch_asym_t<T, 4, true, IdxT>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
+                                           meta, fp_x, st);
+  return launch_asym_t<T, 4, false, IdxT>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
+                                          meta, fp_x, st);
+}
+
+// ---------------------------------------------------------------------------------------------
+// find_meta: one warp per row, 128-bit loads (QUIK src/asymmetric/asymmetric.cu:263-338).
+template <typename T>
+__global__ void find_meta_kernel(const T *__restrict__ src, int rows, int cols, int bits,
+                                 T *__restrict__ meta, int vec) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const T *row = src + (size_t)warp * cols;
+  float mx = -INFINITY, mn = INFINITY;
+  if (vec) {
+    const uint4 *g = reinterpret_cast<const uint4 *>(row);
+    for (int i = lane; i < (cols >> 3); i += 32) {
+      uint4 q = __ldg(g + i);
+      const T *e = reinterpret_cast<const T *>(&q);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float f = Traits<T>::to_float(e[j]);
+        mx = fmaxf(mx, f);
+        mn = fminf(mn, f);
+      }
+    }
+  } else {
+    for (int i = lane; i < cols; i += 32) {
+      const float f = Traits<T>::to_float(row[i]);
+      mx = fmaxf(mx, f);
+      mn = fminf(mn, f);
+    }
+  }
+  mx = warp_max(mx);
+  mn = warp_min(mn);
+  if (lane == 0) {
+    meta[2 * (size_t)warp] = Traits<T>::from_float(fmaxf((mx - mn) / (float)((1 << bits) - 1), 1e-6f));
+    meta[2 * (size_t)warp + 1] = Traits<T>::from_float(mn);
+  }
+}
+
+// quantizeOld: elementwise over a pre-gathered matrix (QUIK src/asymmetric/asymmetric.cu:13-66).
+// One thread per output byte (bits=4: two codes, the odd tail nibble stays 0).
+template <typename T, int BITS>
+__global__ void quantize_old_kernel(const T *__restrict__ src, const T *__restrict__ meta, int rows,
+                                    int cols, uint8_t *__restrict__ dst) {
+  const int cols_dst = BITS == 4 ? (cols + 1) / 2 : cols;
+  const size_t total = (size_t)rows * cols_dst;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / cols_dst), c = (int)(i % cols_dst);
+    const T scale = meta[2 * (size_t)r], zero = meta[2 * (size_t)r + 1];
+    if (BITS == 8) {
+      dst[i] = (uint8_t)(quantize_code<T, 8>(src[(size_t)r * cols + c], zero, scale) & 0xFF);
+    } else {
+      int lo = quantize_code<T, 4>(src[(size_t)r * cols + 2 * c], zero, scale);
+      int hi = (2 * c + 1 < cols) ? quantize_code<T, 4>(src[(size_t)r * cols + 2 * c + 1], zero, scale) : 0;
+      dst[i] = (uint8_t)((lo & 0xF) | ((hi & 0xF) << 4));
+    }
+  }
+}
+
+// symmetric quantize, fp16 (QUIK src/symmetric/symmetric.cu:6-78): rn(hdiv(x, scale[row])), no clamp.
+template <int BITS>
+__global__ void sym_quantize_kernel(const __half *__restrict__ src, const __half *__restrict__ scale,
+                                    int rows, int cols, uint8_t *__restrict__ dst) {
+  const int cols_dst = BITS == 4 ? (cols + 1) / 2 : cols;
+  const size_t total = (size_t)rows * cols_dst;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / cols_dst), c = (int)(i % cols_dst);
+    const __half s = scale[r];
+    if (BITS == 8) {
+      dst[i] = (uint8_t)(__half2int_rn(__hdiv(src[(size_t)r * cols + c], s)) & 0xFF);
+    } else {
+      int lo = __half2int_rn(__hdiv(src[(size_t)r * cols + 2 * c], s));
+      int hi = (2 * c + 1 < cols) ? __half2int_rn(__hdiv(src[(size_t)r * cols + 2 * c + 1], s)) : 0;
+      dst[i] = (uint8_t)((lo & 0xF) | ((hi & 0xF) << 4));
+    }
+  }
+}
+
+inline int ew_grid(size_t total, int threads) {
+  size_t blocks = (total + threads - 1) / threads;
+  size_t cap = (size_t)num_sms() * 16;
+  return (int)max((size_t)1, min(blocks, cap));
+}
+
+}  // namespace
+
+int launch_asym_quantize(const void *src, int dtype, int rows, int cols, const void *int_idx,
+                         int num_int, const void *fp_idx, int num_fp, int idx_bytes, int bits,
+                         int wide, void *dst, void *meta, void *fp_x, cudaStream_t st) {
+  if (rows == 0) return QUIK_OK;
+  if (dtype == QUIK_F16) {
+    return idx_bytes == 8
+               ? dispatch_bits<__half, int64_t>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st)
+               : dispatch_bits<__half, uint16_t>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+  }
+  return idx_bytes == 8
+             ? dispatch_bits<__nv_bfloat16, int64_t>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st)
+             : dispatch_bits<__nv_bfloat16, uint16_t>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+}
+
+int launch_find_meta(const void *src, int dtype, int rows, int cols, int bits, void *meta,
+                     cudaStream_t st) {
+  if (rows == 0) return QUIK_OK;
+  const int threads = 256, grid = (rows * 32 + threads - 1) / threads;
+  const int vec = (cols % 8 == 0) && aligned16(src);
+  if (dtype == QUIK_F16)
+    find_meta_kernel<__half><<<grid, threads, 0, st>>>(static_cast<const __half *>(src), rows, cols, bits, static_cast<__half *>(meta), vec);
+  else
+    find_meta_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(static_cast<const __nv_bfloat16 *>(src), rows, cols, bits, static_cast<__nv_bfloat16 *>(meta), vec);
+  return check_launch("find_meta_kernel");
+}
+
+int launch_quantize_old(const void *src, int dtype, const void *meta, int rows, int cols, int bits,
+                        void *dst, cudaStream_t st) {
+  if (rows == 0 || cols == 0) return QUIK_OK;
+  const size_t total = (size_t)rows * (bits == 4 ? (cols + 1) / 2 : cols);
+  const int threads = 256, grid = ew_grid(total, threads);
+  uint8_t *d = static_cast<uint8_t *>(dst);
+  if (dtype == QUIK_F16) {
+    auto s = static_cast<const __half *>(src), m = static_cast<const __half *>(meta);
+    if (bits == 4) quantize_old_kernel<__half, 4><<<grid, threads, 0, st>>>(s, m, rows, cols, d);
+    else quantize_old_kernel<__half, 8><<<grid, threads, 0, st>>>(s, m, rows, cols, d);
+  } else {
+    auto s = static_cast<const __nv_bfloat16 *>(src), m = static_cast<const __nv_bfloat16 *>(meta);
+    if (bits == 4) quantize_old_kernel<__nv_bfloat16, 4><<<grid, threads, 0, st>>>(s, m, rows, cols, d);
+    else quantize_old_kernel<__nv_bfloat16, 8><<<grid, threads, 0, st>>>(s, m, rows, cols, d);
+  }
+  return check_launch("quantize_old_kernel");
+}
+
+int launch_sym_quantize(const void *src, const void *scale, int rows, int cols, int bits, void *dst,
+                        cudaStream_t st) {
+  if (rows == 0 || cols == 0) return QUIK_OK;
+  const size_t total = (size_t)rows * (bits == 4 ? (cols + 1) / 2 : cols);
+  const int threads = 256, grid = ew_grid(total, threads);
+  auto s = static_cast<const __half *>(src), sc = static_cast<const __half *>(scale);
+  uint8_t *d = static_cast<uint8_t *>(dst);
+  if (bits == 4) sym_quantize_kernel<4><<<grid, threads, 0, st>>>(s, sc, rows, cols, d);
+  else sym_quantize_kernel<8><<<grid, threads, 0, st>>>(s, sc, rows, cols, d);
+  return check_launch("sym_quantize_kernel");
+}
+
+}  // namespace quik

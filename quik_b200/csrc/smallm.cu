@@ -1,0 +1,190 @@
+// Weight-streaming kernel for the small-batch regime (M <= 16 tokens), where the layer is bound
+// by reading the weights from HBM once.  It consumes the weights in their storage format --
+// packed int4 (two codes per byte, QUIK include/int4.h:78-98) or int8 -- straight from global
+// memory into mma.sync fragments, so no unpacked copy of the weights is ever read or written:
+//   int4:  mma.sync.m16n8k64.s4   int8: mma.sync.m16n8k32.s8   outliers: mma.sync.m16n8k16.f16/bf16
+// and applies the dequantize epilogue of QUIK src/asymmetric/asymmetric.cu:134-146 in the same
+// launch (out = T(acc*(s_m*sw_n) + ((z_m + shift*s_m)*wred_n + (acc_fp + bias_n)))).
+//
+// Mapping: the tokens are the 16-row operand, 8 weight rows are the 8-column operand.  A dot
+// product does not depend on the order of its terms, so each lane takes 32 contiguous bytes of a
+// weight row (two 128-bit loads) and of the matching token rows per 128-byte k-block and feeds
+// word j / word j+4 to MMA j: every 128-byte line of the weights is read exactly once, fully
+// coalesced, with identical k-permutation on both operands.  A CTA owns 8 weight rows; its 8
+// warps split the k-blocks (split-K inside the CTA, reduced through shared memory).
+#include "common.cuh"
+
+namespace quik {
+namespace {
+
+constexpr int SM_THREADS = 256, SM_WARPS = 8;
+
+__device__ __forceinline__ uint4 ld_stream(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+template <int BITS>
+__device__ __forceinline__ void mma_int(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+  if (BITS == 4) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k64.row.col.s32.s4.s4.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void mma_fp(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma_fp<__half>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_fp<__nv_bfloat16>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                      uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Two 16-byte pieces (bytes [off, off+16) and [off+16, off+32)) of a row; pieces beyond the row
+// end or of an absent row read as zero.
+__device__ __forceinline__ void load_pair(const uint8_t *row, bool row_ok, int off, int row_bytes, bool stream,
+                                          uint4 &lo, uint4 &hi) {
+  const uint4 z = make_uint4(0, 0, 0, 0);
+  lo = z;
+  hi = z;
+  if (!row_ok) return;
+  if (off + 16 <= row_bytes) lo = stream ? ld_stream(row + off) : __ldg(reinterpret_cast<const uint4 *>(row + off));
+  if (off + 32 <= row_bytes) hi = stream ? ld_stream(row + off + 16) : __ldg(reinterpret_cast<const uint4 *>(row + off + 16));
+}
+
+template <typename T, int BITS>
+__global__ void __launch_bounds__(SM_THREADS)
+small_m_kernel(const uint8_t *__restrict__ q, const uint8_t *__restrict__ w, int M, int N, int row_bytes,
+               const T *__restrict__ fp_x, const T *__restrict__ fp_w, int F, const T *__restrict__ meta,
+               const T *__restrict__ scale_col, const T *__restrict__ wred, const T *__restrict__ bias,
+               T *__restrict__ out) {
+  __shared__ int s_int[SM_WARPS][32][4];
+  __shared__ float s_fp[SM_WARPS][32][4];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * 8;
+  const int wr = min(n0 + g, N - 1);                  // clamped weight row (stores are masked)
+  const bool m_lo = g < M, m_hi = g + 8 < M;
+
+  const int int_blocks = (row_bytes + 127) >> 7;
+  const int fp_bytes = F * (int)sizeof(T);
+  const int fp_blocks = (fp_bytes + 127) >> 7;
+  const int nblocks = int_blocks + fp_blocks;
+
+  const uint8_t *w_row = w + (size_t)wr * row_bytes;
+  const uint8_t *q_lo = q + (size_t)g * row_bytes;
+  const uint8_t *q_hi = q + (size_t)(g + 8) * row_bytes;
+  const uint8_t *fw_row = reinterpret_cast<const uint8_t *>(fp_w) + (size_t)wr * fp_bytes;
+  const uint8_t *fx_lo = reinterpret_cast<const uint8_t *>(fp_x) + (size_t)g * fp_bytes;
+  const uint8_t *fx_hi = reinterpret_cast<const uint8_t *>(fp_x) + (size_t)(g + 8) * fp_bytes;
+
+  int ci[4] = {0, 0, 0, 0};
+  float cf[4] = {0.f, 0.f, 0.f, 0.f};
+
+  // The outlier blocks come first in the block numbering so that they spread over the warps
+  // that would otherwise start one integer block later.
+#pragma unroll 2
+  for (int b = warp; b < nblocks; b += SM_WARPS) {
+    const bool is_fp = b < fp_blocks;
+    const int off = (is_fp ? b : b - fp_blocks) * 128 + t * 32;
+    uint4 wl, wh, al, ah, bl, bh;
+    if (is_fp) {
+      load_pair(fw_row, true, off, fp_bytes, true, wl, wh);
+      load_pair(fx_lo, m_lo, off, fp_bytes, false, al, ah);
+      load_pair(fx_hi, m_hi, off, fp_bytes, false, bl, bh);
+      const uint32_t W0[4] = {wl.x, wl.y, wl.z, wl.w}, W1[4] = {wh.x, wh.y, wh.z, wh.w};
+      const uint32_t A0[4] = {al.x, al.y, al.z, al.w}, A1[4] = {ah.x, ah.y, ah.z, ah.w};
+      const uint32_t B0[4] = {bl.x, bl.y, bl.z, bl.w}, B1[4] = {bh.x, bh.y, bh.z, bh.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) mma_fp<T>(cf, A0[j], B0[j], A1[j], B1[j], W0[j], W1[j]);
+    } else {
+      load_pair(w_row, true, off, row_bytes, true, wl, wh);
+      load_pair(q_lo, m_lo, off, row_bytes, false, al, ah);
+      load_pair(q_hi, m_hi, off, row_bytes, false, bl, bh);
+      const uint32_t W0[4] = {wl.x, wl.y, wl.z, wl.w}, W1[4] = {wh.x, wh.y, wh.z, wh.w};
+      const uint32_t A0[4] = {al.x, al.y, al.z, al.w}, A1[4] = {ah.x, ah.y, ah.z, ah.w};
+      const uint32_t B0[4] = {bl.x, bl.y, bl.z, bl.w}, B1[4] = {bh.x, bh.y, bh.z, bh.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) mma_int<BITS>(ci, A0[j], B0[j], A1[j], B1[j], W0[j], W1[j]);
+    }
+  }
+
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    s_int[warp][lane][r] = ci[r];
+    s_fp[warp][lane][r] = cf[r];
+  }
+  __syncthreads();
+
+  if (threadIdx.x < 128) {
+    const int l = threadIdx.x >> 2, r = threadIdx.x & 3;
+    int acc = 0;
+    float facc = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < SM_WARPS; ++wv) {
+      acc += s_int[wv][l][r];
+      facc += s_fp[wv][l][r];
+    }
+    // accumulator register r of lane l: row (l/4) + 8*(r/2) of the token tile, column 2*(l%4) + (r%2)
+    const int m = (l >> 2) + ((r >> 1) << 3);
+    const int n = n0 + ((l & 3) << 1) + (r & 1);
+    if (m < M && n < N) {
+      const float srow = Traits<T>::to_float(meta[2 * m]);
+      const float zrow = Traits<T>::to_float(meta[2 * m + 1]);
+      const float shift = BITS == 4 ? 8.0f : 128.0f;
+      float add = facc;
+      if (bias) add = __fadd_rn(add, Traits<T>::to_float(bias[n]));
+      add = __fadd_rn(__fmul_rn(__fadd_rn(zrow, __fmul_rn(shift, srow)), Traits<T>::to_float(wred[n])), add);
+      const float res = __fadd_rn(__fmul_rn((float)acc, __fmul_rn(srow, Traits<T>::to_float(scale_col[n]))), add);
+      out[(size_t)m * N + n] = Traits<T>::from_float(res);
+    }
+  }
+}
+
+}  // namespace
+
+int launch_small_m(const void *q, const void *w, int bits, int M, int N, int K_int, const Epilogue &ep,
+                   cudaStream_t st) {
+  if (M == 0 || N == 0) return QUIK_OK;
+  if (M > QUIK_SMALL_M_MAX) return QUIK_ERR_UNSUPPORTED;
+  const int row_bytes = bits == 4 ? K_int / 2 : K_int;
+  if (row_bytes % 16 != 0) return QUIK_ERR_SHAPE;
+  if (!aligned16(q) || !aligned16(w)) return QUIK_ERR_ALIGN;
+  if (ep.F > 0 && (ep.F % 8 != 0 || !aligned16(ep.fp_a) || !aligned16(ep.fp_b))) return QUIK_ERR_ALIGN;
+  if (ep.meta == nullptr || ep.w_reduced == nullptr || ep.y != nullptr) return QUIK_ERR_UNSUPPORTED;
+  const int grid = (N + 7) / 8;
+#define QUIK_SM(T, B)                                                                                     \
+  small_m_kernel<T, B><<<grid, SM_THREADS, 0, st>>>(                                                      \
+      static_cast<const uint8_t *>(q), static_cast<const uint8_t *>(w), M, N, row_bytes,                 \
+      static_cast<const T *>(ep.fp_a), static_cast<const T *>(ep.fp_b), ep.F, static_cast<const T *>(ep.meta), \
+      static_cast<const T *>(ep.scale_col), static_cast<const T *>(ep.w_reduced),                         \
+      static_cast<const T *>(ep.bias), static_cast<T *>(ep.out))
+  if (ep.dtype == QUIK_BF16) { if (bits == 4) QUIK_SM(__nv_bfloat16, 4); else QUIK_SM(__nv_bfloat16, 8); }
+  else { if (bits == 4) QUIK_SM(__half, 4); else QUIK_SM(__half, 8); }
+#undef QUIK_SM
+  return check_launch("small_m_kernel");
+}
+
+}  // namespace quik

@@ -1,0 +1,257 @@
+"""MixedQLinear -- the mixed-precision quantized linear layer, API-compatible with the reference
+module (QUIK experiments/qlinear.py:11-199): same constructor, ``from_float``, buffer names, dtypes
+and shapes (so reference ``state_dict``s load), same ``SharedQuantizedInput`` protocol.
+
+``forward`` runs two launches instead of the reference's five: the activation quantizer and one
+fused kernel (integer GEMM + outlier fp16 GEMM + dequantize).  ``MixedQLinear.fused = False``
+switches to the reference's own operator sequence (quantize -> int matmul -> F.linear ->
+dequantize) on this package's operators.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+from torch import Tensor
+
+from . import _lib, asymmetric, matmul, symmetric
+from ._lib import check, dtype_code, load, ptr, stream_of
+
+__all__ = ["two_compl", "pack_to_i4", "SharedQuantizedInput", "MixedQLinear"]
+
+
+def two_compl(x: Tensor, bits: int) -> Tensor:
+    """Unsigned two's-complement representation of negative values (experiments/qlinear.py:11-12)."""
+    return torch.where(x < 0, 2 ** bits + x, x)
+
+
+def pack_to_i4(X: Tensor) -> Tensor:
+    """Pack int4 values two per byte, even column in the low nibble (experiments/qlinear.py:15-18)."""
+    X_i8 = two_compl(X.to(dtype=torch.int8), 4).to(torch.uint8)
+    return X_i8[:, 0::2] | (X_i8[:, 1::2] << 4)
+
+
+class SharedQuantizedInput:
+    """Quantized-activation cache shared by the layers of one group (q/k/v, gate/up);
+    experiments/qlinear.py:21-37.  The first member quantizes, the others reuse, and the cache is
+    dropped after ``group_size`` calls to :meth:`finish`."""
+
+    def __init__(self, group_size):
+        self.qint_x = None
+        self.fp_x = None
+        self.qscale_x = None
+        self.meta = None
+        self.wide = False          # layout of qint_x: one code per byte (True) or the reference layout
+        self.group_size = group_size
+        self.cur_group_elem = 0
+
+    def finish(self):
+        self.cur_group_elem += 1
+        if self.cur_group_elem == self.group_size:
+            self.qint_x = None
+            self.qscale_x = None
+            self.meta = None
+            self.fp_x = None
+            self.cur_group_elem = 0
+
+
+def _to_u16(idx: Tensor) -> Tensor:
+    """int64 column ids -> the same ids as 16-bit values (stored in an int16 tensor) on idx.device."""
+    a = idx.detach().cpu().numpy().astype(np.uint16)
+    return torch.from_numpy(a.view(np.int16).copy()).to(idx.device)
+
+
+class MixedQLinear(torch.nn.Module):
+    fused = True   # class-wide default; set on an instance to override
+    # optional profiling hook: called as hook(module, begin: bool) right before / after the fused
+    # GEMM launch (on the launching stream), e.g. to record CUDA events
+    launch_hook = None
+
+    def __init__(self, in_features, out_features, shared_input=None,
+                 fp_features_num=0, symm=False, bits=4, dtype=torch.float16):
+        super().__init__()
+        self.fp_features_num = fp_features_num
+        self.int_features_num = in_features - fp_features_num
+        self.in_features = in_features
+        self.out_features = out_features
+        self.symmetric = symm
+        self.bits = bits
+        self.shared_input = shared_input
+        self.dtype = dtype
+        # buffer schema of experiments/qlinear.py:53-78
+        self.register_buffer('weights_scales', torch.zeros((self.out_features, 1), dtype=self.dtype))
+        if self.bits == 4:
+            self.register_buffer('int_weight', torch.randint(1, 7, (self.out_features, self.int_features_num // 2),
+                                                             dtype=torch.uint8))
+        else:
+            self.register_buffer('int_weight', torch.randint(-128, 127, (self.out_features, self.int_features_num),
+                                                             dtype=torch.int8))
+        self.register_buffer('bias', torch.zeros((self.out_features), dtype=dtype))
+        self.register_buffer('int_indices', torch.zeros((self.int_features_num), dtype=torch.long))
+        self.register_buffer('fp_indices', torch.zeros((self.fp_features_num), dtype=torch.long))
+        if self.fp_features_num > 0:
+            self.register_buffer('fp_weight', torch.randint(-8, 7, (self.out_features, self.fp_features_num)).to(dtype))
+        if not self.symmetric:
+            self.register_buffer('reduced_w', torch.zeros((1, self.out_features), dtype=dtype))
+        self._cache = {}
+
+    # ------------------------------------------------------------------ derived, lazily built operands
+    def _cached(self, name, src: Tensor, make):
+        key = (src.data_ptr(), src._version, str(src.device))
+        ent = self._cache.get(name)
+        if ent is None or ent[0] != key:
+            ent = (key, make(src))
+            self._cache[name] = ent
+        return ent[1]
+
+    def _idx16(self):
+        return (self._cached("int16", self.int_indices, _to_u16), self._cached("fp16", self.fp_indices, _to_u16))
+
+    def _weight_codes_int8(self):
+        """Weight codes one per byte, the operand layout of the tensor-core engine."""
+        if self.bits == 8:
+            return self.int_weight
+        return self._cached("w8", self.int_weight, matmul.unpack_int4)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, x):
+        if self.int_features_num <= 0:
+            return torch.nn.functional.linear(x, self.fp_weight, self.bias)
+        if torch.cuda.current_device() != x.device.index:
+            torch.cuda.set_device(x.device)
+
+        shared_input = self.shared_input
+        if shared_input is None:
+            shared_input = SharedQuantizedInput(1)
+        if len(x.shape) == 3:
+            x = x[0]
+        if self.symmetric:
+            return self._forward_symmetric(x, shared_input)
+        if not self.fused:
+            return self._forward_unfused(x, shared_input)
+
+        M = x.shape[0]
+        wide = M > _lib.SMALL_M_MAX          # tensor-core engine above, weight streaming below
+        if shared_input.qint_x is None:
+            i16, f16 = self._idx16()
+            shared_input.qint_x, shared_input.meta, shared_input.fp_x = asymmetric.quantize_u16(
+                x, i16, f16, self.bits, wide)
+            shared_input.wide = wide
+        q = shared_input.qint_x
+        packed = self.bits == 4 and not shared_input.wide
+        w = self.int_weight if (packed or self.bits == 8) else self._weight_codes_int8()
+        N = self.out_features
+        hook = MixedQLinear.launch_hook
+        with torch.cuda.device(x.device):
+            out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+            F = self.fp_features_num
+            if hook is not None:
+                hook(self, True)
+            check(load().quik_mixed_linear(
+                ptr(q), int(packed), ptr(w), int(packed), ptr(shared_input.meta), ptr(self.weights_scales),
+                ptr(self.reduced_w), ptr(shared_input.fp_x) if F > 0 else None,
+                ptr(self.fp_weight) if F > 0 else None, ptr(self.bias) if self.bias is not None else None,
+                ptr(out), dtype_code(x.dtype), M, N, self.int_features_num, F, self.bits, stream_of(x)),
+                "MixedQLinear.forward")
+            if hook is not None:
+                hook(self, False)
+        shared_input.finish()
+        return out.reshape((1, *out.shape))
+
+    def _forward_unfused(self, x, shared_input):
+        """The reference's operator sequence (experiments/qlinear.py:105-148)."""
+        if shared_input.qint_x is None:
+            shared_input.qint_x, shared_input.meta, shared_input.fp_x = asymmetric.quantize(
+                x, self.int_indices, self.fp_indices, self.bits)
+            shared_input.wide = False
+        if self.fp_features_num > 0:
+            fp_result = torch.nn.functional.linear(shared_input.fp_x, self.fp_weight, self.bias)
+        elif self.bias is not None:
+            fp_result = self.bias.repeat(shared_input.qint_x.shape[0], 1)
+        else:
+            fp_result = torch.zeros((shared_input.qint_x.shape[0], self.out_features), dtype=x.dtype, device=x.device)
+        if self.bits == 4:
+            int_result = matmul.int4Matmul(shared_input.qint_x, self.int_weight)
+        else:
+            int_result = matmul.int8Matmul(shared_input.qint_x, self.int_weight)
+        output = asymmetric.dequantize(int_result, shared_input.meta, self.weights_scales, self.reduced_w,
+                                       fp_result, self.bits)
+        shared_input.finish()
+        return output.reshape((1, *output.shape))
+
+    def _forward_symmetric(self, x, shared_input):
+        """Symmetric-activation branch (experiments/qlinear.py:94-103,141-142).  The reference calls
+        quik.symmetric.quantize / dequantize without their ``bits`` argument there, which raises
+        TypeError against its own extension; this passes ``bits`` (and 32 for the int32 accumulator)."""
+        if shared_input.qint_x is None:
+            if self.fp_features_num > 0:
+                int_x = x[:, self.int_indices].contiguous()
+                shared_input.fp_x = x[:, self.fp_indices].contiguous()
+            else:
+                int_x = x
+            reshaped_x = int_x.reshape((-1, int_x.shape[-1]))
+            shared_input.qscale_x = (torch.max(torch.abs(reshaped_x), dim=1)[0].unsqueeze(1) / (
+                    1 << (self.bits - 1) - 1)).to(torch.float16)
+            shared_input.qint_x = symmetric.quantize(int_x, shared_input.qscale_x, self.bits)
+        if self.fp_features_num > 0:
+            fp_result = torch.nn.functional.linear(shared_input.fp_x, self.fp_weight, self.bias)
+        elif self.bias is not None:
+            fp_result = self.bias.repeat(shared_input.qint_x.shape[0], 1)
+        else:
+            fp_result = torch.zeros((shared_input.qint_x.shape[0], self.out_features), dtype=x.dtype, device=x.device)
+        if self.bits == 4:
+            int_result = matmul.int4Matmul(shared_input.qint_x, self.int_weight)
+        else:
+            int_result = matmul.int8Matmul(shared_input.qint_x, self.int_weight)
+        output = symmetric.dequantize(int_result, shared_input.qscale_x, self.weights_scales.reshape(1, -1).contiguous(),
+                                      fp_result, 32)
+        shared_input.finish()
+        return output.reshape((1, *output.shape))
+
+    # ------------------------------------------------------------------ construction
+    @staticmethod
+    def from_float(module: torch.nn.Linear, weight_matrix, weights_scales, shared_input=None,
+                   fp_indices=None, symm=False, bits=4):
+        """Build the layer from a float ``nn.Linear`` (experiments/qlinear.py:150-199).
+
+        ``weight_matrix`` holds the (already rounded-to-grid) weights, ``weights_scales`` the
+        per-output-channel scale [out_features, 1].  Integer columns are stored as
+        ``round(W / scale)`` (packed two per byte for 4 bits), outlier columns verbatim, and
+        ``reduced_w`` is the fp32 row sum of the integer-column weights.
+        """
+        assert weights_scales.shape == (module.out_features, 1), 'weights_scales should have shape (out_features, 1)'
+        assert weight_matrix.shape == (module.out_features, module.in_features)
+        assert (symm and bits == 4) or not symm, "Symmetric quantization with 8 bits is not supported"
+        int_indices = torch.arange(module.in_features)
+        if fp_indices is None or len(fp_indices) == 0:
+            fp_indices = torch.tensor([], dtype=int_indices.dtype)
+        else:
+            fp_indices = fp_indices.cpu()
+            int_indices = int_indices[~torch.isin(int_indices, fp_indices)]
+        assert torch.numel(int_indices) + torch.numel(fp_indices) == module.in_features, \
+            'There are some duplication in the fp_indices!'
+
+        int_module = MixedQLinear(module.in_features, module.out_features, shared_input,
+                                  fp_features_num=torch.numel(fp_indices), symm=symm, bits=bits,
+                                  dtype=weight_matrix.dtype)
+        if torch.cuda.is_available():
+            weight_matrix = weight_matrix.cuda()
+        dev = weight_matrix.device
+        int_module.weights_scales.copy_(weights_scales.to(weight_matrix.dtype))
+        int_rounded_weight = (weight_matrix[:, int_indices.to(dev)] / weights_scales.to(dev)).round()
+        if bits == 4:
+            int_module.int_weight.copy_(pack_to_i4(int_rounded_weight.to(torch.int8)).cpu())
+        else:
+            int_module.int_weight.copy_(int_rounded_weight.to(torch.int8).cpu())
+        if not symm:
+            reduced_w = torch.sum(weight_matrix[:, int_indices.to(dev)].float(), dim=1, keepdim=True).to(
+                weight_matrix.dtype)
+            int_module.reduced_w.copy_(reduced_w.t().cpu())
+        if module.bias is not None:
+            int_module.bias.copy_(module.bias)
+        else:
+            int_module.bias = None
+        int_module.int_indices.copy_(int_indices)
+        int_module.fp_indices.copy_(fp_indices)
+        if int_module.fp_features_num > 0:
+            int_module.fp_weight.copy_(weight_matrix[:, fp_indices.to(dev)].to(weight_matrix.dtype))
+        return int_module

@@ -1,0 +1,95 @@
+"""GPU parity: exact int32 GEMMs (both engines) and the fused GEMM+dequantize ops."""
+import pytest
+import torch
+
+from oracle import kernel_path as kp
+from quik_b200 import _lib
+from tests.gpu_util import assert_device_clean, dev
+
+pytestmark = pytest.mark.gpu
+
+ENGINES = [("mma_sync", _lib.ENGINE_MMA_SYNC, 0), ("tcgen05_auto", _lib.ENGINE_TCGEN05, 0),
+           ("tcgen05_n128", _lib.ENGINE_TCGEN05, 128), ("tcgen05_n256", _lib.ENGINE_TCGEN05, 256)]
+
+
+@pytest.fixture(params=ENGINES, ids=[e[0] for e in ENGINES])
+def engine(request):
+    _, eng, tile = request.param
+    _lib.set_engine(eng)
+    _lib.set_tile_n(tile)
+    yield request.param[0]
+    torch.cuda.synchronize()
+    assert_device_clean()
+    _lib.set_engine(_lib.ENGINE_AUTO)
+    _lib.set_tile_n(0)
+
+
+SHAPES = [(128, 256, 128), (1, 8, 16), (3, 20, 48), (129, 260, 3840), (512, 32, 512), (300, 520, 10752),
+          (2048, 4096, 4096), (17, 4100, 176)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_int8_matmul_exact(engine, M, N, K):
+    import quik
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8)
+    b = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8)
+    # canary-padded output: the kernel must write exactly [M, N]
+    c = quik.matmul.int8Matmul(a.to(dev()), b.to(dev()))
+    ref = kp.int8_matmul(a, b)
+    assert torch.equal(c.cpu(), ref)
+    c2 = quik.matmul.int8Matmul(a.to(dev()), b.to(dev()))
+    assert torch.equal(c2, c)
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 32, 512), (64, 136, 3840), (2048, 512, 4096), (5, 24, 64)])
+def test_int4_matmul_exact(engine, M, N, K):
+    """test/python/test_matmul.py:16-26 (first shape) and ragged / Llama-sized variants."""
+    import quik
+    g = torch.Generator().manual_seed(K)
+    a = torch.randint(-8, 8, (M, K), generator=g, dtype=torch.int8)
+    b = torch.randint(-8, 8, (N, K), generator=g, dtype=torch.int8)
+    c_gt = (a.float() @ b.float().t()).round().to(torch.int32)
+    c = quik.matmul.int4Matmul(kp.pack_to_i4(a).to(dev()), kp.pack_to_i4(b).to(dev()))
+    assert torch.equal(c.cpu(), c_gt)
+
+
+def _fused_inputs(bits, M, N, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    lo, hi = (-3, 3)
+    a = torch.randint(lo, hi, (M, K), generator=g, dtype=torch.int8)
+    b = torch.randint(lo, hi, (N, K), generator=g, dtype=torch.int8)
+    sr = torch.rand(M, 1, generator=g).half()
+    sc = torch.rand(1, N, generator=g).half()
+    zr = torch.rand(M, 1, generator=g).half()
+    wr = torch.rand(1, N, generator=g).half()
+    y = torch.rand(M, N, generator=g).half()
+    return a, b, sr, sc, zr, wr, y
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("M,N,K", [(1024, 5120, 2048), (100, 72, 256)])
+def test_fused_dequantize_ops(engine, bits, M, N, K):
+    """test/python/test_fused.py:16-67,130-177.  The reference asserts equality with a formula whose
+    every operation is rounded to fp16; this implementation evaluates it in fp32 with one rounding,
+    so it must equal the fp32 formula exactly and the reference formula within 3 fp16 ulps."""
+    import quik
+    a, b, sr, sc, zr, wr, y = _fused_inputs(bits, M, N, K, seed=2)
+    sv = 0.4376
+    acc = kp.int8_matmul(a, b)
+    qa, qb = (kp.pack_to_i4(a), kp.pack_to_i4(b)) if bits == 4 else (a, b)
+    d = dev()
+    asym = quik.asymmetric.int4FusedDequantize if bits == 4 else quik.asymmetric.int8FusedDequantize
+    sym = quik.symmetric.int4FusedDequantize if bits == 4 else quik.symmetric.int8FusedDequantize
+    out = asym(qa.to(d), qb.to(d), sr.to(d), sc.to(d), sv, zr.to(d), wr.to(d), y.to(d)).cpu()
+    f32 = (acc.float() * (sr.float() * sc.float()) + ((zr.float() + torch.tensor(sv) * sr.float()) * wr.float() + y.float())).half()
+    assert torch.equal(out, f32)
+    ref16 = kp.asym_fused_dequantize_fp16(acc, sr, sc, sv, zr, wr, y)
+    ulp = torch.maximum(ref16.abs().float() * 2 ** -10, torch.tensor(2.0 ** -24))
+    assert ((out.float() - ref16.float()).abs() <= 3 * ulp).all()
+    out_s = sym(qa.to(d), qb.to(d), sr.to(d), sc.to(d), y.to(d)).cpu()
+    f32s = (acc.float() * (sr.float() * sc.float()) + y.float()).half()
+    assert torch.equal(out_s, f32s)
+    ref16s = kp.sym_fused_dequantize_fp16(acc, sr, sc, y)
+    ulp = torch.maximum(ref16s.abs().float() * 2 ** -10, torch.tensor(2.0 ** -24))
+    assert ((out_s.float() - ref16s.float()).abs() <= 3 * ulp).all()

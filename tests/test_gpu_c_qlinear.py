@@ -1,0 +1,116 @@
+"""GPU parity: MixedQLinear.forward (fused, unfused, shared input, small-M, bf16) vs the CPU oracle."""
+import pytest
+import torch
+
+from oracle import kernel_path as kp
+from quik_b200 import _lib
+from quik_b200.qlinear import MixedQLinear, SharedQuantizedInput
+from quik_b200.workloads import make_layer
+from tests.gpu_util import assert_device_clean, dev, rel_rms_err
+
+pytestmark = pytest.mark.gpu
+
+# BASELINE tolerance: max-abs error of the fp16 output relative to the output RMS
+TOL_RMS = 1e-2
+
+
+def _oracle_out(case, round_y):
+    m = case.module
+    buf = {"int_weight": m.int_weight.cpu(), "weights_scales": m.weights_scales.cpu(), "reduced_w": m.reduced_w.cpu(),
+           "int_indices": m.int_indices.cpu(), "fp_indices": m.fp_indices.cpu(),
+           "bias": None if m.bias is None else m.bias.cpu()}
+    if m.fp_features_num > 0:
+        buf["fp_weight"] = m.fp_weight.cpu()
+    return kp.mixed_linear_forward(case.x.cpu(), buf, m.bits, round_y=round_y)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,N,F,bits", [
+    (1, 4096, 512, 256, 4), (16, 4096, 264, 256, 4), (16, 1024, 128, 0, 8), (7, 11008, 256, 256, 8),
+    (17, 4096, 512, 256, 4), (129, 4096, 520, 256, 4), (256, 1024, 384, 0, 4), (128, 11008, 256, 256, 8),
+    (2048, 4096, 1024, 256, 4), (300, 8192, 1024, 1024, 4), (64, 96, 40, 32, 4),
+])
+def test_fused_forward_matches_oracle(dtype, M, K, N, F, bits):
+    case = make_layer("t", M, K, N, bits, F=F, seed=M + N, device=dev(), dtype=dtype, clip=False)
+    out = case.module(case.x.unsqueeze(0))
+    assert out.shape == (1, M, N) and out.dtype == dtype
+    ref = _oracle_out(case, round_y=False)
+    err = rel_rms_err(out[0].cpu(), ref)
+    tol = TOL_RMS if dtype == torch.float16 else 2e-2      # bf16 has 3 fewer mantissa bits
+    assert err < tol, err
+    ref_rounded = _oracle_out(case, round_y=True)           # the reference's own unfused rounding of y
+    assert rel_rms_err(out[0].cpu(), ref_rounded) < tol
+    out2 = case.module(case.x.unsqueeze(0))
+    assert torch.equal(out, out2)                            # deterministic
+    assert_device_clean()
+
+
+@pytest.mark.parametrize("M,bits,F", [(64, 4, 256), (5, 8, 0), (200, 8, 256)])
+def test_unfused_forward_matches_oracle(M, bits, F):
+    case = make_layer("t", M, 4096, 256, bits, F=F, seed=3, device=dev(), clip=False)
+    case.module.fused = False
+    out = case.module(case.x.unsqueeze(0))[0].cpu()
+    ref = _oracle_out(case, round_y=True)
+    # same int32 accumulators and same fp32 epilogue; only the cuBLAS outlier GEMM may round differently
+    assert rel_rms_err(out, ref) < 2e-3
+    case.module.fused = True
+    fused = case.module(case.x.unsqueeze(0))[0].cpu()
+    assert rel_rms_err(fused, out) < TOL_RMS
+
+
+def test_bias_and_no_outliers():
+    torch.manual_seed(0)
+    K, N, M = 512, 128, 40
+    lin = torch.nn.Linear(K, N, bias=True)
+    w = (0.02 * torch.randn(N, K)).half()
+    scales = w.float().abs().max(1, keepdim=True)[0] / 7
+    mod = MixedQLinear.from_float(lin, w, scales, fp_indices=None, bits=4).to(dev())
+    x = torch.randn(M, K).half().to(dev())
+    out = mod(x.unsqueeze(0))[0].cpu()
+    buf = kp.from_float_buffers(w, scales, None, 4, bias=lin.bias.data.half())
+    ref = kp.mixed_linear_forward(x.cpu(), buf, 4, round_y=True)
+    assert torch.equal(out, ref)      # no outlier GEMM: integer GEMM + fp32 epilogue is bit exact
+    for name in ("int_weight", "weights_scales", "reduced_w", "int_indices", "bias"):
+        assert torch.equal(getattr(mod, name).cpu(), buf[name]), name
+
+
+def test_shared_quantized_input_groups():
+    """q/k/v style group of three layers shares one quantizer call (experiments/llama.py:402-411)."""
+    shared = SharedQuantizedInput(3)
+    cases = [make_layer(f"m{i}", 48, 1024, 128, 4, F=64, seed=0, device=dev(), shared_input=shared, clip=False)
+             for i in range(3)]
+    x = cases[0].x
+    outs = []
+    for i, c in enumerate(cases):
+        outs.append(c.module(x.unsqueeze(0)))
+        if i < 2:
+            assert shared.qint_x is not None and shared.cur_group_elem == i + 1
+    assert shared.qint_x is None and shared.cur_group_elem == 0
+    for c, o in zip(cases, outs):
+        solo = make_layer("s", 48, 1024, 128, 4, F=64, seed=0, device=dev(), clip=False)
+        assert torch.equal(o, solo.module(x.unsqueeze(0)))
+
+
+def test_state_dict_round_trip():
+    case = make_layer("t", 32, 1024, 128, 4, F=64, seed=1, device=dev(), clip=False)
+    sd = case.module.state_dict()
+    fresh = MixedQLinear(1024, 128, fp_features_num=64, bits=4)
+    fresh.bias = None
+    fresh.load_state_dict(sd)
+    fresh = fresh.to(dev())
+    assert torch.equal(fresh(case.x.unsqueeze(0)), case.module(case.x.unsqueeze(0)))
+
+
+def test_symmetric_branch_runs():
+    torch.manual_seed(0)
+    K, N, M = 256, 64, 16
+    lin = torch.nn.Linear(K, N, bias=False)
+    w = torch.randint(-7, 8, (N, K)).half()
+    mod = MixedQLinear.from_float(lin, w, torch.ones(N, 1), fp_indices=None, symm=True, bits=4).to(dev())
+    x = torch.randn(M, K).half().to(dev())
+    out = mod(x.unsqueeze(0))[0].cpu()
+    qs = (x.abs().max(1)[0].unsqueeze(1) / (1 << (4 - 1) - 1)).half().cpu()
+    q = kp.sym_quantize(x.cpu(), qs, 4)
+    acc = kp.int4_matmul(q, kp.pack_to_i4(w.to(torch.int8)))
+    ref = kp.sym_dequantize(acc, qs, torch.ones(1, N).half(), torch.zeros(M, N).half(), 32)
+    assert torch.equal(out, ref)
