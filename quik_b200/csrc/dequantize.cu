@@ -66,7 +66,9 @@ __global__ void sym_dequantize_kernel(const X *__restrict__ x, const __half *__r
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
     const int r = (int)(i / cols), c = (int)(i % cols);
-    out[i] = __hadd(__hmul(__hmul(to_half_rn<X>(x[i]), srow[r]), scol[c]), y[i]);
+    // _rn forms: never contracted into a fused multiply-add, so each operation rounds like the torch
+    // expression the reference asserts against (test/python/test_cuaprseLt.py:44-47)
+    out[i] = __hadd_rn(__hmul_rn(__hmul_rn(to_half_rn<X>(x[i]), srow[r]), scol[c]), y[i]);
   }
 }
 

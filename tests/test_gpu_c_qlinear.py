@@ -38,8 +38,10 @@ def test_fused_forward_matches_oracle(dtype, M, K, N, F, bits):
     err = rel_rms_err(out[0].cpu(), ref)
     tol = TOL_RMS if dtype == torch.float16 else 2e-2      # bf16 has 3 fewer mantissa bits
     assert err < tol, err
-    ref_rounded = _oracle_out(case, round_y=True)           # the reference's own unfused rounding of y
-    assert rel_rms_err(out[0].cpu(), ref_rounded) < tol
+    # the reference's own unfused sequence rounds the outlier product to the storage type before the
+    # dequantize step; in bf16 that extra rounding alone is worth up to 2^-8 of |y|
+    ref_rounded = _oracle_out(case, round_y=True)
+    assert rel_rms_err(out[0].cpu(), ref_rounded) < (tol if dtype == torch.float16 else 2 * tol)
     out2 = case.module(case.x.unsqueeze(0))
     assert torch.equal(out, out2)                            # deterministic
     assert_device_clean()
