@@ -130,13 +130,12 @@ gemm_mma_sync_kernel(const int8_t *__restrict__ A, const int8_t *__restrict__ B,
           if (ep.mode == 0) {
             ep.C[off] = v;
           } else {
+            // same fused multiply-add formula as the tcgen05 engine's epilogue
             const float scol = ld_f<T>(ep.scale_col, col);
             float add = ep.y ? ld_f<T>(ep.y, off) : 0.f;
-            if (ep.bias) add = __fadd_rn(add, ld_f<T>(ep.bias, col));
-            if (ep.w_reduced)
-              add = __fadd_rn(__fmul_rn(__fadd_rn(zrow, __fmul_rn(ep.shift_value, srow)),
-                                        ld_f<T>(ep.w_reduced, col)), add);
-            const float r = __fadd_rn(__fmul_rn((float)v, __fmul_rn(srow, scol)), add);
+            if (ep.bias) add += ld_f<T>(ep.bias, col);
+            if (ep.w_reduced) add = fmaf(fmaf(ep.shift_value, srow, zrow), ld_f<T>(ep.w_reduced, col), add);
+            const float r = fmaf((float)v, srow * scol, add);
             static_cast<T *>(ep.out)[off] = Traits<T>::from_float(r);
           }
         }

@@ -35,8 +35,8 @@ namespace {
 
 constexpr int BLOCK_M = 128;
 constexpr int STAGE_K_BYTES = 128;           // one 128B-swizzle row of K per stage
-constexpr int NUM_THREADS = 192;
-constexpr int TMEM_COLS = 512;
+constexpr int NUM_THREADS = 320;              // TMA warp + MMA warp + 8 epilogue warps
+constexpr int NUM_EPI_THREADS = 256;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s per wait
 int g_tile_n = 0;                                             // 0 = choose by shape
 
@@ -182,7 +182,47 @@ template <typename T> __device__ __forceinline__ float ldf(const void *p, size_t
   return Traits<T>::to_float(static_cast<const T *>(p)[i]);
 }
 
+// 32 consecutive values of type T: 16-byte vector access when `vec`, scalar with a column guard
+// otherwise.
+template <typename T>
+__device__ __forceinline__ void load_row32(const T *src, bool vec, int ncols_left, T (&v)[32]) {
+  if (vec) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) reinterpret_cast<uint4 *>(v)[j] = reinterpret_cast<const uint4 *>(src)[j];
+  } else {
+    for (int j = 0; j < 32; ++j) v[j] = (j < ncols_left) ? src[j] : Traits<T>::from_float(0.f);
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store_row32(T *dst, bool vec, int ncols_left, const float (&o)[32]) {
+  if (vec) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 pk;
+      T *pe = reinterpret_cast<T *>(&pk);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) pe[e] = Traits<T>::from_float(o[8 * j + e]);
+      reinterpret_cast<uint4 *>(dst)[j] = pk;
+    }
+  } else {
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols_left) dst[j] = Traits<T>::from_float(o[j]);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
+// Work of one CTA = its tiles t_0, t_1, ... (tile index blockIdx.x + j * gridDim.x).  TMEM holds
+// two accumulator regions of BLOCK_N columns; tile j uses region j & 1 for BOTH of its products,
+// one after the other:
+//   FP(t_j):  outlier k-blocks -> region (f32), drained by the epilogue warps, which round
+//             (product + bias) to T and park it in the tile's place in `out` (it stays in L2);
+//   INT(t_j): integer k-blocks -> same region (s32), then the final epilogue reads the parked
+//             value back (same thread, same address), applies the dequantize arithmetic and
+//             overwrites it.
+// The MMA issue order is FP(t_0), then for every j: first half of INT(t_j), FP(t_{j+1}), second half
+// of INT(t_j).  FP(t_{j+1}) and its drain therefore run in the shadow of INT(t_j), and the epilogue of
+// t_j in the shadow of INT(t_{j+1}): the tensor pipe never waits for an epilogue in steady state
+// although int32 and fp32 accumulators cannot share a region at the same time.
 template <typename T, int BLOCK_N, bool HAS_FP>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -192,8 +232,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   constexpr int B_BYTES = BLOCK_N * STAGE_K_BYTES;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int STAGES = (BLOCK_N == 256) ? 4 : 6;
-  constexpr int ACC_COLS = BLOCK_N * (HAS_FP ? 2 : 1);        // TMEM columns per accumulator stage
-  constexpr int ACC_STAGES = (TMEM_COLS / ACC_COLS) >= 2 ? 2 : 1;
+  constexpr int TMEM_ALLOC = 2 * BLOCK_N;                     // two accumulator regions
+  constexpr int HALF_N = BLOCK_N / 2;                         // columns per epilogue warp
 
   extern __shared__ unsigned char smem_dyn[];
   // 128B-swizzled tiles need 1024-byte alignment
@@ -201,12 +241,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   unsigned char *aux = tiles + STAGES * STAGE_BYTES;
   uint64_t *full_bar = reinterpret_cast<uint64_t *>(aux);               // [STAGES]
   uint64_t *empty_bar = full_bar + STAGES;                             // [STAGES]
-  uint64_t *tmem_full = empty_bar + STAGES;                            // [ACC_STAGES]
-  uint64_t *tmem_empty = tmem_full + ACC_STAGES;                       // [ACC_STAGES]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + ACC_STAGES);
+  uint64_t *acc_full = empty_bar + STAGES;                             // [2] integer product complete
+  uint64_t *acc_empty = acc_full + 2;                                  // [2] region free again
+  uint64_t *fp_full = acc_empty + 2;                                   // [2] outlier product complete
+  uint64_t *fp_drained = fp_full + 2;                                  // [2] outlier product parked
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(fp_drained + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   // per-column epilogue vectors, one private copy per epilogue warp (no cross-warp barrier needed)
-  float *s_vec = reinterpret_cast<float *>(aux + 256);                 // [4][3][BLOCK_N], 16-byte aligned
+  float *s_vec = reinterpret_cast<float *>(aux + 256);                 // [8][3][HALF_N], 16-byte aligned
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -215,9 +257,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       mbar_init(smem_u32(full_bar + s), 1);
       mbar_init(smem_u32(empty_bar + s), 1);
     }
-    for (int s = 0; s < ACC_STAGES; ++s) {
-      mbar_init(smem_u32(tmem_full + s), 1);
-      mbar_init(smem_u32(tmem_empty + s), 128);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(acc_full + s), 1);
+      mbar_init(smem_u32(acc_empty + s), NUM_EPI_THREADS);
+      mbar_init(smem_u32(fp_full + s), 1);
+      mbar_init(smem_u32(fp_drained + s), NUM_EPI_THREADS);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -230,7 +274,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_alloc(smem_u32(tmem_slot), TMEM_ALLOC);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -238,7 +282,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int nkb = p.int_kb + (HAS_FP ? p.fp_kb : 0);
+  const int n_local = (p.num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // tiles of this CTA
+  const int int_half = (p.int_kb + 1) / 2;
 
   if (warp == 0) {
     // ================= TMA producer =================
@@ -246,171 +291,211 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      // one k-block range of one product of tile j into the ring
+      auto feed = [&](int j, bool fp, int kb0, int kb1) {
+        const int tile = blockIdx.x + j * gridDim.x;
         const int m0 = (tile % p.num_m_tiles) * BLOCK_M;
         const int n0 = (tile / p.num_m_tiles) * BLOCK_N;
-        for (int kb = 0; kb < nkb; ++kb) {
+        for (int kb = kb0; kb < kb1 && ok; ++kb) {
           if (!mbar_wait(smem_u32(empty_bar + stage), phase ^ 1, abort_flag)) { ok = false; break; }
           const uint32_t fb = smem_u32(full_bar + stage);
           const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
-          const uint32_t sb = sa + A_BYTES;
           mbar_expect_tx(fb, STAGE_BYTES);
-          if (HAS_FP && kb < p.fp_kb) {
+          if (fp) {
             tma_load_2d(sa, &tmap_fa, fb, kb * 64, m0);
-            tma_load_2d(sb, &tmap_fb, fb, kb * 64, n0);
+            tma_load_2d(sa + A_BYTES, &tmap_fb, fb, kb * 64, n0);
           } else {
-            const int k0 = (kb - (HAS_FP ? p.fp_kb : 0)) * STAGE_K_BYTES;
-            tma_load_2d(sa, &tmap_a, fb, k0, m0);
-            tma_load_2d(sb, &tmap_b, fb, k0, n0);
+            tma_load_2d(sa, &tmap_a, fb, kb * STAGE_K_BYTES, m0);
+            tma_load_2d(sa + A_BYTES, &tmap_b, fb, kb * STAGE_K_BYTES, n0);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
+      };
+      if (HAS_FP && n_local > 0) feed(0, true, 0, p.fp_kb);
+      for (int j = 0; j < n_local && ok; ++j) {
+        feed(j, false, 0, int_half);
+        if (HAS_FP && j + 1 < n_local) feed(j + 1, true, 0, p.fp_kb);
+        feed(j, false, int_half, p.int_kb);
       }
     }
   } else if (warp == 1) {
     // ================= MMA issuer =================
     if (lane == 0) {
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
+      int stage = 0;
+      uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait(smem_u32(tmem_empty + acc), acc_phase ^ 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t d_int = tmem_base + acc * ACC_COLS;
-        const uint32_t d_fp = d_int + BLOCK_N;
-        for (int kb = 0; kb < nkb; ++kb) {
+      auto issue = [&](int j, bool fp, int kb0, int kb1) {
+        const int r = j & 1;
+        const uint32_t use_parity = (uint32_t)(j >> 1) & 1u;
+        const uint32_t d = tmem_base + r * BLOCK_N;
+        for (int kb = kb0; kb < kb1 && ok; ++kb) {
+          if (kb == 0) {
+            // the region must be free: after the previous tile's epilogue (outlier product, or
+            // integer product of an outlier-free layer), or after this tile's drain
+            const bool after_drain = HAS_FP && !fp;
+            const uint32_t bar = smem_u32((after_drain ? fp_drained : acc_empty) + r);
+            if (!mbar_wait(bar, after_drain ? use_parity : (use_parity ^ 1u), abort_flag)) { ok = false; break; }
+            tc_fence_after();
+          }
           if (!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
-          const bool is_fp = HAS_FP && kb < p.fp_kb;
-          const int kb_local = is_fp ? kb : kb - (HAS_FP ? p.fp_kb : 0);
 #pragma unroll
           for (int k = 0; k < STAGE_K_BYTES / 32; ++k) {
             // +32 bytes of K inside the swizzled row = +2 in the 16-byte start-address field
-            const uint32_t accumulate = (kb_local > 0 || k > 0) ? 1u : 0u;
-            if (is_fp) mma_f16(d_fp, da + 2 * k, db + 2 * k, p.idesc_fp, accumulate);
-            else mma_i8(d_int, da + 2 * k, db + 2 * k, p.idesc_int, accumulate);
+            const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+            if (fp) mma_f16(d, da + 2 * k, db + 2 * k, p.idesc_fp, accumulate);
+            else mma_i8(d, da + 2 * k, db + 2 * k, p.idesc_int, accumulate);
           }
           mma_commit(smem_u32(empty_bar + stage));          // stage reusable once these MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (fp && kb == p.fp_kb - 1) mma_commit(smem_u32(fp_full + r));
+          if (!fp && kb == p.int_kb - 1) mma_commit(smem_u32(acc_full + r));
         }
-        if (!ok) break;
-        mma_commit(smem_u32(tmem_full + acc));               // accumulator complete -> epilogue
-        if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+      };
+      if (HAS_FP && n_local > 0) issue(0, true, 0, p.fp_kb);
+      for (int j = 0; j < n_local && ok; ++j) {
+        issue(j, false, 0, int_half);
+        if (HAS_FP && j + 1 < n_local) issue(j + 1, true, 0, p.fp_kb);
+        issue(j, false, int_half, p.int_kb);
       }
     }
   } else {
-    // ================= epilogue (warps 2..5) =================
+    // ================= epilogue (warps 2..9) =================
+    const int e = warp - 2;
     const int sub = warp & 3;                 // TMEM lane quarter this warp may read
-    float *s_scol = s_vec + (warp - 2) * 3 * BLOCK_N;
-    float *s_wred = s_scol + BLOCK_N;
-    float *s_bias = s_wred + BLOCK_N;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+    const int half = e >> 2;                  // which half of the tile's columns
+    float *s_scol = s_vec + e * 3 * HALF_N;
+    float *s_wred = s_scol + HALF_N;
+    float *s_bias = s_wred + HALF_N;
+    bool ok = true;
+
+    // park T(outlier product + bias) of tile j in `out`
+    auto drain = [&](int j) {
+      const int tile = blockIdx.x + j * gridDim.x;
       const int m0 = (tile % p.num_m_tiles) * BLOCK_M;
-      const int n0 = (tile / p.num_m_tiles) * BLOCK_N;
+      const int n0 = (tile / p.num_m_tiles) * BLOCK_N + half * HALF_N;
+      const int r = j & 1;
+      __syncwarp();
+      for (int c = lane; c < HALF_N; c += 32)
+        s_bias[c] = (n0 + c < p.N && p.bias) ? ldf<T>(p.bias, n0 + c) : 0.f;
+      __syncwarp();
+      const bool ready = mbar_wait(smem_u32(fp_full + r), (uint32_t)(j >> 1) & 1u, abort_flag);
+      if (!__all_sync(0xffffffffu, ready)) { ok = false; return; }
+      tc_fence_after();
+      const int row = m0 + sub * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + r * BLOCK_N + half * HALF_N;
+#pragma unroll 1
+      for (int c0 = 0; c0 < HALF_N; c0 += 32) {
+        uint32_t f[32];
+        __syncwarp();                          // tcgen05.ld is warp-collective
+        tmem_ld32(taddr + c0, f);
+        tmem_ld_wait();
+        const int col0 = n0 + c0;
+        if (row < p.M && col0 < p.N) {
+          float o[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(f[i]) + s_bias[c0 + i];
+          store_row32<T>(static_cast<T *>(p.out) + (size_t)row * p.N + col0, p.vec_out && col0 + 32 <= p.N,
+                         p.N - col0, o);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(fp_drained + r));
+    };
+
+    auto finish = [&](int j) {
+      const int tile = blockIdx.x + j * gridDim.x;
+      const int m0 = (tile % p.num_m_tiles) * BLOCK_M;
+      const int n0 = (tile / p.num_m_tiles) * BLOCK_N + half * HALF_N;
+      const int r = j & 1;
       if (p.mode == 1) {
-        __syncwarp();                         // previous tile's vector reads are done
-        for (int c = lane; c < BLOCK_N; c += 32) {
+        __syncwarp();                         // previous readers of the vectors are done
+        for (int c = lane; c < HALF_N; c += 32) {
           const int col = n0 + c;
           const bool in = col < p.N;
           s_scol[c] = in ? ldf<T>(p.scale_col, col) : 0.f;
           s_wred[c] = (in && p.w_reduced) ? ldf<T>(p.w_reduced, col) : 0.f;
-          s_bias[c] = (in && p.bias) ? ldf<T>(p.bias, col) : 0.f;
+          s_bias[c] = (in && p.bias && !HAS_FP) ? ldf<T>(p.bias, col) : 0.f;   // with outliers the drain added it
         }
         __syncwarp();
       }
-      // warp-uniform outcome: tcgen05.ld below is warp-collective
-      const bool ready = mbar_wait(smem_u32(tmem_full + acc), acc_phase, abort_flag);
-      if (!__all_sync(0xffffffffu, ready)) break;
+      const bool ready = mbar_wait(smem_u32(acc_full + r), (uint32_t)(j >> 1) & 1u, abort_flag);
+      if (!__all_sync(0xffffffffu, ready)) { ok = false; return; }
       tc_fence_after();
-
       const int row = m0 + sub * 32 + lane;
       const bool row_ok = row < p.M;
       float srow = 0.f, zs = 0.f;
       if (p.mode == 1 && row_ok) {
         srow = ldf<T>(p.row_scale, (size_t)row * p.row_stride);
         const float zrow = p.row_zero ? ldf<T>(p.row_zero, (size_t)row * p.row_stride) : 0.f;
-        zs = __fadd_rn(zrow, __fmul_rn(p.shift_value, srow));
+        zs = fmaf(p.shift_value, srow, zrow);
       }
-      const uint32_t t_int = tmem_base + ((uint32_t)(sub * 32) << 16) + acc * ACC_COLS;
-
+      const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + r * BLOCK_N + half * HALF_N;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
+      for (int c0 = 0; c0 < HALF_N; c0 += 32) {
         uint32_t v[32];
-        uint32_t f[32];
         __syncwarp();                          // tcgen05.ld is warp-collective: reconverge first
-        tmem_ld32(t_int + c0, v);
-        if (HAS_FP) tmem_ld32(t_int + BLOCK_N + c0, f);
+        tmem_ld32(taddr + c0, v);
         tmem_ld_wait();
         const int col0 = n0 + c0;
+        if (!row_ok || col0 >= p.N) continue;
         const bool full_chunk = col0 + 32 <= p.N;
         const size_t off = (size_t)row * p.N + col0;
-        if (!row_ok || col0 >= p.N) {
-          // nothing to store for this thread
-        } else if (p.mode == 0) {
+        if (p.mode == 0) {
           if (full_chunk && p.vec_out) {
             int4 *dst = reinterpret_cast<int4 *>(p.C + off);
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              dst[j] = make_int4((int)v[4 * j], (int)v[4 * j + 1], (int)v[4 * j + 2], (int)v[4 * j + 3]);
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_int4((int)v[4 * i], (int)v[4 * i + 1], (int)v[4 * i + 2], (int)v[4 * i + 3]);
           } else {
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) p.C[off + j] = (int)v[j];
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) p.C[off + i] = (int)v[i];
           }
+          continue;
+        }
+        float add[32];
+        if (HAS_FP) {
+          T parked[32];
+          load_row32<T>(static_cast<const T *>(p.out) + off, full_chunk && p.vec_out, p.N - col0, parked);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) add[i] = Traits<T>::to_float(parked[i]);
         } else {
-          float o[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) add[i] = s_bias[c0 + i];
+        }
+        if (p.y != nullptr) {
           T yv[32];
-          const bool has_y = p.y != nullptr;
-          if (has_y) {
-            if (full_chunk && p.vec_y) {
-              const uint4 *ys = reinterpret_cast<const uint4 *>(static_cast<const T *>(p.y) + off);
+          load_row32<T>(static_cast<const T *>(p.y) + off, full_chunk && p.vec_y, p.N - col0, yv);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) reinterpret_cast<uint4 *>(yv)[j] = __ldg(ys + j);
-            } else {
-              for (int j = 0; j < 32; ++j)
-                yv[j] = (col0 + j < p.N) ? static_cast<const T *>(p.y)[off + j] : Traits<T>::from_float(0.f);
-            }
-          }
+          for (int i = 0; i < 32; ++i) add[i] += Traits<T>::to_float(yv[i]);
+        }
+        float o[32];
 #pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            const float4 sc4 = reinterpret_cast<const float4 *>(s_scol + c0)[j4];
-            const float4 wr4 = reinterpret_cast<const float4 *>(s_wred + c0)[j4];
-            const float4 bi4 = reinterpret_cast<const float4 *>(s_bias + c0)[j4];
-            const float sc[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
-            const float wr[4] = {wr4.x, wr4.y, wr4.z, wr4.w};
-            const float bi[4] = {bi4.x, bi4.y, bi4.z, bi4.w};
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 sc4 = reinterpret_cast<const float4 *>(s_scol + c0)[i4];
+          const float4 wr4 = reinterpret_cast<const float4 *>(s_wred + c0)[i4];
+          const float sc[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
+          const float wr[4] = {wr4.x, wr4.y, wr4.z, wr4.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = 4 * j4 + e;
-              float add = HAS_FP ? __uint_as_float(f[j]) : 0.f;
-              add = __fadd_rn(add, bi[e]);
-              if (has_y) add = __fadd_rn(add, Traits<T>::to_float(yv[j]));
-              add = __fadd_rn(__fmul_rn(zs, wr[e]), add);
-              o[j] = __fadd_rn(__fmul_rn((float)(int)v[j], __fmul_rn(srow, sc[e])), add);
-            }
-          }
-          T *dst = static_cast<T *>(p.out) + off;
-          if (full_chunk && p.vec_out) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 pk;
-              T *pe = reinterpret_cast<T *>(&pk);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) pe[e] = Traits<T>::from_float(o[8 * j + e]);
-              reinterpret_cast<uint4 *>(dst)[j] = pk;
-            }
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) dst[j] = Traits<T>::from_float(o[j]);
+          for (int q = 0; q < 4; ++q) {
+            const int i = 4 * i4 + q;
+            // out = acc * (s_row * s_col) + ((zero + shift * s_row) * w_red + addend), fused multiply-adds
+            o[i] = fmaf((float)(int)v[i], srow * sc[q], fmaf(zs, wr[q], add[i]));
           }
         }
+        store_row32<T>(static_cast<T *>(p.out) + off, full_chunk && p.vec_out, p.N - col0, o);
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(tmem_empty + acc));
-      if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+      mbar_arrive(smem_u32(acc_empty + r));
+    };
+
+    if (HAS_FP && n_local > 0) drain(0);
+    for (int j = 0; j < n_local && ok; ++j) {
+      if (HAS_FP && j + 1 < n_local) drain(j + 1);
+      if (!ok) break;
+      finish(j);
     }
   }
 
@@ -424,7 +509,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    tmem_dealloc(tmem_base, TMEM_ALLOC);
   }
 }
 
@@ -482,7 +567,7 @@ template <int BLOCK_N>
 constexpr size_t smem_bytes() {
   constexpr int stages = (BLOCK_N == 256) ? 4 : 6;
   return 1024 /*align slack*/ + (size_t)stages * (BLOCK_M + BLOCK_N) * STAGE_K_BYTES +
-         256 /*barriers, TMEM slot, abort flag*/ + 4 * 3 * BLOCK_N * 4 /*epilogue vectors*/;
+         256 /*barriers, TMEM slot, abort flag*/ + 8 * 3 * (BLOCK_N / 2) * 4 /*epilogue vectors*/;
 }
 
 template <typename T, int BLOCK_N, bool HAS_FP>

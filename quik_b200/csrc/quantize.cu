@@ -6,10 +6,12 @@
 // min, code = clamp(rn(hdiv(hsub(x, zero), scale)), 0, 2^b-1) - 2^(b-1), outlier columns copied.
 //
 // Design for B200: the reference reads every row three times through 8-byte indices with 2-byte
-// loads and one 1024-thread block per row.  Here a CTA keeps the column ids in shared memory as
-// 16-bit values for its whole lifetime, streams each row from HBM exactly once with 128-bit
-// loads into shared memory, and does min/max (warp shuffles), quantize+pack and the outlier
-// gather from that copy.  HBM traffic per row: cols*2 bytes in, codes + outliers + meta out.
+// loads, one 1024-thread block per row and block-wide barriers.  Here a CTA keeps the column ids
+// in shared memory as 16-bit values for its whole lifetime and every warp owns whole rows: it
+// streams a row from HBM exactly once (16-byte cp.async into its private shared-memory buffer)
+// and does min/max (warp shuffles only), quantize+pack and the outlier gather from that copy, so
+// no block-wide barrier sits on the row loop.  HBM traffic per row: cols*2 bytes in, codes +
+// outliers + meta out.
 #include "common.cuh"
 
 namespace quik {
@@ -29,67 +31,75 @@ __device__ __forceinline__ int quantize_code(T x, T zero, T scale) {
   return min(max(v, 0), kMaxQ) - kShift;
 }
 
-// Block-wide max/min of per-thread partials; every thread receives the result.
-__device__ __forceinline__ void block_minmax(float &mx, float &mn, float *red /* [2*warps] */) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  mx = warp_max(mx);
-  mn = warp_min(mn);
-  if (lane == 0) {
-    red[warp] = mx;
-    red[nwarps + warp] = mn;
-  }
-  __syncthreads();
-  mx = red[0];
-  mn = red[nwarps];
-  for (int w = 1; w < nwarps; ++w) {
-    mx = fmaxf(mx, red[w]);
-    mn = fminf(mn, red[nwarps + w]);
-  }
-  __syncthreads();
-}
-
-// IdxT: int64_t (reference ABI) or uint16_t (layer-cached ids).
+// One warp per row.  IdxT: int64_t (reference ABI) or uint16_t (layer-cached ids).
+// Shared memory: [column ids of the CTA, 16-bit][one private row buffer per warp].
 template <typename T, int BITS, bool WIDE, typename IdxT>
 __global__ void __launch_bounds__(kQuantThreads)
 asym_quantize_kernel(const T *__restrict__ src, const IdxT *__restrict__ int_idx,
                      const IdxT *__restrict__ fp_idx, int rows, int cols, int num_int, int num_fp,
                      uint8_t *__restrict__ dst, T *__restrict__ meta, T *__restrict__ fp_x,
-                     int vec_load, int vec_store) {
+                     int vec_load, int vec_store, int warps_per_cta) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int num_chunks = (num_int + 7) >> 3;           // 8 codes per chunk
   const int int_pad = num_chunks << 3;
-  uint16_t *s_int = reinterpret_cast<uint16_t *>(smem_raw);               // [int_pad]
-  uint16_t *s_fp = s_int + int_pad;                                       // [num_fp rounded to 8]
   const int fp_pad = (num_fp + 7) & ~7;
-  T *s_row = reinterpret_cast<T *>(s_fp + fp_pad);                        // [cols rounded to 8]
   const int cols_pad = (cols + 7) & ~7;
-  float *s_red = reinterpret_cast<float *>(s_row + cols_pad);             // [2 * warps]
+  uint16_t *s_int = reinterpret_cast<uint16_t *>(smem_raw);               // [int_pad]
+  uint16_t *s_fp = s_int + int_pad;                                       // [fp_pad]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  T *s_row = reinterpret_cast<T *>(s_fp + fp_pad) + (size_t)warp * cols_pad;   // this warp's row
 
-  const int tid = threadIdx.x;
-  // column ids -> shared memory, once per CTA; the pad of the last chunk repeats the first id so
-  // that it never changes the row's max/min.
-  for (int i = tid; i < int_pad; i += kQuantThreads)
-    s_int[i] = static_cast<uint16_t>(i < num_int ? int_idx[i] : int_idx[0]);
-  for (int i = tid; i < num_fp; i += kQuantThreads) s_fp[i] = static_cast<uint16_t>(fp_idx[i]);
+  // Column ids -> shared memory, once per CTA; the pad of the last chunk repeats the first id so
+  // that it never changes the row's max/min.  16-bit ids are copied eight at a time; every warp
+  // first puts the copy of its first row in flight so that both latencies overlap.
+  const int first_row = blockIdx.x + gridDim.x * warp;
+  const bool prefetched = vec_load && warp < warps_per_cta && first_row < rows;
+  if (prefetched) {
+    const unsigned sbase = (unsigned)__cvta_generic_to_shared(s_row);
+    const uint4 *g = reinterpret_cast<const uint4 *>(src + (size_t)first_row * cols);
+    for (int i = lane; i < (cols >> 3); i += 32)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sbase + i * 16), "l"(g + i));
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  }
+  if (sizeof(IdxT) == 2 && (num_int & 7) == 0 && (reinterpret_cast<uintptr_t>(int_idx) & 15) == 0) {
+    const uint4 *g = reinterpret_cast<const uint4 *>(int_idx);
+    uint4 *d = reinterpret_cast<uint4 *>(s_int);
+    for (int i = tid; i < (num_int >> 3); i += blockDim.x) d[i] = __ldg(g + i);
+  } else {
+#pragma unroll 4
+    for (int i = tid; i < int_pad; i += blockDim.x)
+      s_int[i] = static_cast<uint16_t>(i < num_int ? int_idx[i] : int_idx[0]);
+  }
+  for (int i = tid; i < num_fp; i += blockDim.x) s_fp[i] = static_cast<uint16_t>(fp_idx[i]);
+  __syncthreads();
+  if (warp >= warps_per_cta) return;
 
-  constexpr int kBytesPerChunk = (BITS == 4 && !WIDE) ? 4 : 8;
   const size_t dst_pitch = (BITS == 4 && !WIDE) ? (size_t)(num_int >> 1) : (size_t)num_int;
+  // rows are dealt round-robin over the CTAs first, then over the warps of a CTA, so that a
+  // short matrix still spreads over all SMs
+  const int row_stride = gridDim.x * warps_per_cta;
 
-  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+  for (int r = blockIdx.x + gridDim.x * warp; r < rows; r += row_stride) {
     const T *row = src + (size_t)r * cols;
-    __syncthreads();   // previous row fully consumed (and ids visible on the first trip)
-    if (vec_load) {
-      const uint4 *g = reinterpret_cast<const uint4 *>(row);
-      uint4 *s = reinterpret_cast<uint4 *>(s_row);
-      for (int i = tid; i < (cols >> 3); i += kQuantThreads) s[i] = __ldg(g + i);
+    __syncwarp();   // previous row fully consumed by every lane
+    if (prefetched && r == first_row) {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    } else if (vec_load) {
+      // global -> shared without a register round trip
+      const unsigned sbase = (unsigned)__cvta_generic_to_shared(s_row);
+      for (int i = lane; i < (cols >> 3); i += 32)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sbase + i * 16),
+                     "l"(reinterpret_cast<const uint4 *>(row) + i));
+      asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
     } else {
-      for (int i = tid; i < cols; i += kQuantThreads) s_row[i] = row[i];
+      for (int i = lane; i < cols; i += 32) s_row[i] = row[i];
     }
-    __syncthreads();
+    __syncwarp();
 
     // ---- pass 1: max / min over the gathered integer columns
     float mx = -INFINITY, mn = INFINITY;
-    for (int c = tid; c < num_chunks; c += kQuantThreads) {
+#pragma unroll 2
+    for (int c = lane; c < num_chunks; c += 32) {
       const uint4 idv = *reinterpret_cast<const uint4 *>(s_int + (c << 3));
       const uint32_t w[4] = {idv.x, idv.y, idv.z, idv.w};
 #pragma unroll
@@ -100,17 +110,19 @@ asym_quantize_kernel(const T *__restrict__ src, const IdxT *__restrict__ int_idx
         mn = fminf(mn, fminf(a, b));
       }
     }
-    block_minmax(mx, mn, s_red);
+    mx = warp_max(mx);
+    mn = warp_min(mn);
     const T scale = Traits<T>::from_float(fmaxf((mx - mn) / (float)((1 << BITS) - 1), 1e-6f));
     const T zero = Traits<T>::from_float(mn);           // exact: mn is a value of type T
-    if (tid == 0) {
+    if (lane == 0) {
       meta[2 * (size_t)r] = scale;
       meta[2 * (size_t)r + 1] = zero;
     }
 
     // ---- pass 2: quantize + pack
     uint8_t *drow = dst + (size_t)r * dst_pitch;
-    for (int c = tid; c < num_chunks; c += kQuantThreads) {
+#pragma unroll 2
+    for (int c = lane; c < num_chunks; c += 32) {
       const uint4 idv = *reinterpret_cast<const uint4 *>(s_int + (c << 3));
       const uint32_t w[4] = {idv.x, idv.y, idv.z, idv.w};
       int v[8];
@@ -144,11 +156,10 @@ asym_quantize_kernel(const T *__restrict__ src, const IdxT *__restrict__ int_idx
         }
       }
     }
-    (void)kBytesPerChunk;
 
     // ---- outlier columns, verbatim
     T *frow = fp_x + (size_t)r * num_fp;
-    for (int j = tid; j < num_fp; j += kQuantThreads) frow[j] = s_row[s_fp[j]];
+    for (int j = lane; j < num_fp; j += 32) frow[j] = s_row[s_fp[j]];
   }
 }
 
@@ -158,16 +169,21 @@ int launch_asym_t(const void *src, int rows, int cols, const void *int_idx, int 
                   cudaStream_t st) {
   const int int_pad = ((num_int + 7) >> 3) << 3, fp_pad = (num_fp + 7) & ~7,
             cols_pad = (cols + 7) & ~7;
-  const size_t smem = (size_t)(int_pad + fp_pad) * 2 + (size_t)cols_pad * sizeof(T) +
-                      2 * (kQuantThreads / 32) * sizeof(float);
+  const size_t idx_bytes = (size_t)(int_pad + fp_pad) * 2, row_bytes = (size_t)cols_pad * sizeof(T);
+  // as many warps (rows in flight) per CTA as shared memory allows, at most 8
+  const size_t budget = 200 * 1024;
+  int warps = (int)((budget - idx_bytes) / row_bytes);
+  if (warps < 1) return QUIK_ERR_UNSUPPORTED;
+  if (warps > kQuantThreads / 32) warps = kQuantThreads / 32;
+  // small rows: keep the CTA at 8 warps but do not let one CTA hog an SM's shared memory
+  const size_t smem = idx_bytes + (size_t)warps * row_bytes;
   auto kern = asym_quantize_kernel<T, BITS, WIDE, IdxT>;
   if (smem > 48 * 1024)
     QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int per_sm = 1;
   QUIK_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kQuantThreads, smem));
   if (per_sm < 1) return QUIK_ERR_UNSUPPORTED;
-  // A few CTAs per SM hide the load latency; more would only repeat the id staging.
-  const int grid = max(1, min(rows, num_sms() * min(per_sm, 4)));
+  const int grid = max(1, min(rows, num_sms() * per_sm));
   const int vec_load = (cols % 8 == 0) && aligned16(src);
   const bool packed = (BITS == 4 && !WIDE);
   const int vec_store = (num_int % 8 == 0) &&
@@ -175,7 +191,7 @@ int launch_asym_t(const void *src, int rows, int cols, const void *int_idx, int 
   kern<<<grid, kQuantThreads, smem, st>>>(
       static_cast<const T *>(src), static_cast<const IdxT *>(int_idx),
       static_cast<const IdxT *>(fp_idx), rows, cols, num_int, num_fp, static_cast<uint8_t *>(dst),
-      static_cast<T *>(meta), static_cast<T *>(fp_x), vec_load, vec_store);
+      static_cast<T *>(meta), static_cast<T *>(fp_x), vec_load, vec_store, warps);
   return check_launch("asym_quantize_kernel");
 }
 
