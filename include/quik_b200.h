@@ -47,6 +47,8 @@ extern "C" {
 #define QUIK_CFG_TILE_N        2
 /* 1 (default): int8 layers with M <= QUIK_SMALL_M_MAX use the weight-streaming engine; 0: never. */
 #define QUIK_CFG_SMALL_M       3
+/* CTA pairs (cta_group::2, 256-row tiles) in the tcgen05 engine: 0 = when M > 128, 1 = never, 2 = always. */
+#define QUIK_CFG_CTA_PAIR      4
 
 const char *quik_version(void);
 const char *quik_strerror(int status);
@@ -58,6 +60,12 @@ int quik_config_get(int key);
  * per-device status word and returns early.  This call synchronises the current device, returns
  * QUIK_OK or QUIK_ERR_DEVICE_WAIT, and clears the word when `clear` is non-zero. */
 int quik_device_status(int clear);
+/* Diagnostics: when `device_buffer` (16 x uint64 per launched CTA, caller-owned device memory) is
+ * non-NULL, every tcgen05 GEMM launch writes per-CTA cycle counters there: [0] MMA issue loop,
+ * [1] of which waiting for a free accumulator region, [2] waiting for operands, [3] tiles of the CTA,
+ * [4] epilogue waiting for an outlier product, [5] waiting for an integer product, [6] parking outlier
+ * products, [7] final epilogues.  NULL switches it off (default).  No reference counterpart. */
+int quik_debug_counters(void *device_buffer);
 
 /* ==== asymmetric activation quantizer ======================================================
  * Replaces quik.asymmetric.quantize (src/asymmetric/asymmetric.cpp:16-25, kernel

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libquik_b200.so")
 
 QUIK_OK = 0
 F16, BF16 = 0, 1
-CFG_GEMM_ENGINE, CFG_TILE_N, CFG_SMALL_M = 1, 2, 3
+CFG_GEMM_ENGINE, CFG_TILE_N, CFG_SMALL_M, CFG_CTA_PAIR = 1, 2, 3, 4
 ENGINE_AUTO, ENGINE_TCGEN05, ENGINE_MMA_SYNC = 0, 1, 2
 SMALL_M_MAX = 16
 
@@ -29,6 +29,7 @@ SIGNATURES = {
     "quik_config_set": (_i, [_i, _i]),
     "quik_config_get": (_i, [_i]),
     "quik_device_status": (_i, [_i]),
+    "quik_debug_counters": (_i, [_vp]),
     "quik_asym_quantize": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp]),
     "quik_asym_quantize_u16": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "quik_asym_find_meta": (_i, [_vp, _i, _i, _i, _i, _vp, _vp]),
@@ -111,6 +112,11 @@ def set_engine(engine: int) -> None:
 
 def set_tile_n(n: int) -> None:
     check(load().quik_config_set(CFG_TILE_N, n), "quik_config_set")
+
+
+def set_cta_pair(mode: int) -> None:
+    """0 = CTA pairs when M > 128, 1 = never, 2 = always."""
+    check(load().quik_config_set(CFG_CTA_PAIR, mode), "quik_config_set")
 
 
 def set_small_m(on: bool) -> None:

@@ -78,17 +78,28 @@ int quik_config_set(int key, int value) {
     g_small_m = value ? 1 : 0;
     return QUIK_OK;
   }
+  if (key == QUIK_CFG_CTA_PAIR) {
+    if (value < 0 || value > 2) return QUIK_ERR_UNSUPPORTED;
+    set_cta_pair(value);
+    return QUIK_OK;
+  }
   return QUIK_ERR_UNSUPPORTED;
 }
 
 int quik_config_get(int key) {
   if (key == QUIK_CFG_SMALL_M) return g_small_m;
+  if (key == QUIK_CFG_CTA_PAIR) return get_cta_pair();
   if (key == QUIK_CFG_GEMM_ENGINE) return g_engine;
   if (key == QUIK_CFG_TILE_N) return get_tile_n();
   return QUIK_ERR_UNSUPPORTED;
 }
 
 int quik_device_status(int clear) { return device_status_read(clear); }
+
+int quik_debug_counters(void *device_buffer) {
+  set_debug_counters(device_buffer);
+  return QUIK_OK;
+}
 
 static int check_quantize_args(const void *src, int dtype, int rows, int cols, const void *int_idx, int num_int,
                                const void *fp_idx, int num_fp, int bits, void *dst, void *meta, void *fp_x) {

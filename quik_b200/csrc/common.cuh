@@ -37,6 +37,9 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 int device_status_read(int clear);   // synchronises the device
 void set_tile_n(int n);               // 0 = by shape, 128 or 256
 int get_tile_n();
+void set_cta_pair(int mode);           // 0 = by shape, 1 = never, 2 = always
+int get_cta_pair();
+void set_debug_counters(void *buf);    // device buffer of 16 x uint64 per CTA, or NULL
 
 // ---- dtype traits ---------------------------------------------------------------------------
 template <typename T> struct Traits;

@@ -39,6 +39,23 @@ constexpr int NUM_THREADS = 320;              // TMA warp + MMA warp + 8 epilogu
 constexpr int NUM_EPI_THREADS = 256;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s per wait
 int g_tile_n = 0;                                             // 0 = choose by shape
+int g_cta_pair = 0;                                           // 0 = by shape, 1 = never, 2 = always
+unsigned long long *g_dbg = nullptr;                          // diagnostic counters (device memory), off by default
+
+// Shared-memory plan after the 1024-byte aligned ring of stages: 256 bytes of barriers etc. and the
+// per-warp epilogue vectors (rounded to 1024 together), then one output staging chunk per epilogue
+// warp (32 rows x 64 bytes).
+constexpr int EPI_BUF_BYTES = 32 * 64;
+constexpr int AUX_BYTES(int block_n) { return ((256 + 8 * 3 * (block_n / 2) * 4) + 1023) / 1024 * 1024; }
+constexpr int stage_bytes(int block_n, int ctas) { return (BLOCK_M + block_n / ctas) * STAGE_K_BYTES; }
+constexpr int SMEM_LIMIT = 227 * 1024;
+constexpr int epi_bufs(int, int) { return 1; }
+// Ring depth: as many stages as fit (at most 8).
+constexpr int num_stages(int block_n, int ctas) {
+  const int n = (SMEM_LIMIT - 1024 - AUX_BYTES(block_n) - 8 * epi_bufs(block_n, ctas) * EPI_BUF_BYTES) /
+                stage_bytes(block_n, ctas);
+  return n > 8 ? 8 : n;
+}
 
 struct GemmParams {
   int M, N;
@@ -55,6 +72,7 @@ struct GemmParams {
   float shift_value;
   int vec_out;                    // 16-byte stores allowed (pitch and base aligned)
   int vec_y;
+  unsigned long long *dbg;         // optional per-CTA cycle counters (16 per CTA), NULL = off
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -108,12 +126,37 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return true;
 }
 
+// In a CTA pair the shared::cluster address of CTA 1 differs from CTA 0's in bit 24; clearing it
+// turns the address of a local barrier into the address of the leader's barrier at the same offset.
+constexpr uint32_t LEADER_ADDR_MASK = 0xFEFFFFFFu;
+
+template <int CTAS>
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
                                             int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
+  if (CTAS == 1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+  } else {
+    // destination in this CTA, completion bytes counted on the pair leader's barrier
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar & LEADER_ADDR_MASK), "r"(c0), "r"(c1)
+        : "memory");
+  }
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on the pair leader's barrier (from either CTA of the pair)
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar & LEADER_ADDR_MASK) : "memory");
 }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -122,35 +165,60 @@ __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// TMEM allocation; with CTAS == 2 the same warp of both CTAs of the pair executes it together.
+template <int CTAS>
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols)
-               : "memory");
+  if (CTAS == 1)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  else
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
 }
+template <int CTAS>
 __device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if (CTAS == 1) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  else asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
 }
+template <int CTAS>
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+  if (CTAS == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+  else asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
-// D[tmem] (+)= A[smem] * B[smem]; `accumulate` = 0 overwrites D.
+// D[tmem] (+)= A[smem] * B[smem]; `accumulate` = 0 overwrites D.  With CTAS == 2 the leader CTA
+// issues one instruction for the pair: M = 256 (128 rows of A from each CTA's shared memory, same
+// offset), N columns of B split in halves over the two CTAs, accumulator rows split likewise.
+template <int CTAS>
 __device__ __forceinline__ void mma_i8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
-      : "memory");
+  if (CTAS == 1)
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+  else
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
+template <int CTAS>
 __device__ __forceinline__ void mma_f16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
-      : "memory");
+  if (CTAS == 1)
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+  else
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
-// Arrive on an mbarrier once all tcgen05.mma issued so far by this thread have completed.
+// Arrive on an mbarrier once all tcgen05.mma issued so far by this thread have completed; with
+// CTAS == 2 the arrival goes to the barrier at this offset in both CTAs of the pair.
+template <int CTAS>
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
+  if (CTAS == 1) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  } else {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(both) : "memory");
+  }
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
@@ -193,23 +261,25 @@ __device__ __forceinline__ void load_row32(const T *src, bool vec, int ncols_lef
     for (int j = 0; j < 32; ++j) v[j] = (j < ncols_left) ? src[j] : Traits<T>::from_float(0.f);
   }
 }
+// eight fp32 values -> eight values of type T in one 16-byte word
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float *o) {
+  uint4 pk;
+  T *pe = reinterpret_cast<T *>(&pk);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) pe[e] = Traits<T>::from_float(o[e]);
+  return pk;
+}
 template <typename T>
 __device__ __forceinline__ void store_row32(T *dst, bool vec, int ncols_left, const float (&o)[32]) {
   if (vec) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint4 pk;
-      T *pe = reinterpret_cast<T *>(&pk);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) pe[e] = Traits<T>::from_float(o[8 * j + e]);
-      reinterpret_cast<uint4 *>(dst)[j] = pk;
-    }
+    for (int j = 0; j < 4; ++j) reinterpret_cast<uint4 *>(dst)[j] = pack8<T>(o + 8 * j);
   } else {
     for (int j = 0; j < 32; ++j)
       if (j < ncols_left) dst[j] = Traits<T>::from_float(o[j]);
   }
 }
-
 // ---------------------------------------------------------------------------------------------
 // Work of one CTA = its tiles t_0, t_1, ... (tile index blockIdx.x + j * gridDim.x).  TMEM holds
 // two accumulator regions of BLOCK_N columns; tile j uses region j & 1 for BOTH of its products,
@@ -223,17 +293,24 @@ __device__ __forceinline__ void store_row32(T *dst, bool vec, int ncols_left, co
 // of INT(t_j).  FP(t_{j+1}) and its drain therefore run in the shadow of INT(t_j), and the epilogue of
 // t_j in the shadow of INT(t_{j+1}): the tensor pipe never waits for an epilogue in steady state
 // although int32 and fp32 accumulators cannot share a region at the same time.
-template <typename T, int BLOCK_N, bool HAS_FP>
+//
+// CTAS == 2: two CTAs on neighbouring SMs (a cluster of 2) work on one 256 x BLOCK_N tile.  Each
+// loads its own 128 rows of A and only its half of the B rows, so a CTA moves a third less operand
+// data per multiply-accumulate than alone.  The leader (cluster rank 0) issues the MMAs for the pair
+// and owns the barriers that count loads and region releases; commits reach both CTAs.
+template <typename T, int BLOCK_N, bool HAS_FP, int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_fa, const __grid_constant__ CUtensorMap tmap_fb,
                     const GemmParams p) {
   constexpr int A_BYTES = BLOCK_M * STAGE_K_BYTES;
-  constexpr int B_BYTES = BLOCK_N * STAGE_K_BYTES;
+  constexpr int B_ROWS = BLOCK_N / CTAS;                      // B rows this CTA loads per k-block
+  constexpr int B_BYTES = B_ROWS * STAGE_K_BYTES;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr int STAGES = (BLOCK_N == 256) ? 4 : 6;
+  constexpr int STAGES = num_stages(BLOCK_N, CTAS);
   constexpr int TMEM_ALLOC = 2 * BLOCK_N;                     // two accumulator regions
   constexpr int HALF_N = BLOCK_N / 2;                         // columns per epilogue warp
+  constexpr int TILE_M = BLOCK_M * CTAS;
 
   extern __shared__ unsigned char smem_dyn[];
   // 128B-swizzled tiles need 1024-byte alignment
@@ -249,6 +326,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   // per-column epilogue vectors, one private copy per epilogue warp (no cross-warp barrier needed)
   float *s_vec = reinterpret_cast<float *>(aux + 256);                 // [8][3][HALF_N], 16-byte aligned
+  // output staging: [8 warps][32 rows x 64 bytes], 1024-byte aligned
+  constexpr int EPI_BUFS = epi_bufs(BLOCK_N, CTAS);
+  unsigned char *s_out = tiles + STAGES * STAGE_BYTES + AUX_BYTES(BLOCK_N);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -259,9 +339,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(acc_full + s), 1);
-      mbar_init(smem_u32(acc_empty + s), NUM_EPI_THREADS);
+      mbar_init(smem_u32(acc_empty + s), NUM_EPI_THREADS * CTAS);    // epilogue threads of the whole pair
       mbar_init(smem_u32(fp_full + s), 1);
-      mbar_init(smem_u32(fp_drained + s), NUM_EPI_THREADS);
+      mbar_init(smem_u32(fp_drained + s), NUM_EPI_THREADS * CTAS);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -274,15 +354,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), TMEM_ALLOC);
-    tmem_relinquish();
+    tmem_alloc<CTAS>(smem_u32(tmem_slot), TMEM_ALLOC);
+    tmem_relinquish<CTAS>();
   }
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync_all();          // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int n_local = (p.num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // tiles of this CTA
+  const int rank = CTAS == 2 ? (int)cluster_ctarank() : 0;
+  const int unit = (int)blockIdx.x / CTAS, num_units = (int)gridDim.x / CTAS;    // a unit = CTA or CTA pair
+  const int n_local = (p.num_tiles - unit + num_units - 1) / num_units;           // tiles of this unit
   const int int_half = (p.int_kb + 1) / 2;
 
   if (warp == 0) {
@@ -293,20 +376,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       bool ok = true;
       // one k-block range of one product of tile j into the ring
       auto feed = [&](int j, bool fp, int kb0, int kb1) {
-        const int tile = blockIdx.x + j * gridDim.x;
-        const int m0 = (tile % p.num_m_tiles) * BLOCK_M;
-        const int n0 = (tile / p.num_m_tiles) * BLOCK_N;
+        const int tile = unit + j * num_units;
+        const int m0 = (tile % p.num_m_tiles) * TILE_M + rank * BLOCK_M;      // this CTA's rows of A
+        const int n0 = (tile / p.num_m_tiles) * BLOCK_N + rank * B_ROWS;      // this CTA's rows of B
         for (int kb = kb0; kb < kb1 && ok; ++kb) {
           if (!mbar_wait(smem_u32(empty_bar + stage), phase ^ 1, abort_flag)) { ok = false; break; }
           const uint32_t fb = smem_u32(full_bar + stage);
           const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
-          mbar_expect_tx(fb, STAGE_BYTES);
+          if (rank == 0) mbar_expect_tx(fb, STAGE_BYTES * CTAS);               // bytes of the whole pair
           if (fp) {
-            tma_load_2d(sa, &tmap_fa, fb, kb * 64, m0);
-            tma_load_2d(sa + A_BYTES, &tmap_fb, fb, kb * 64, n0);
+            tma_load_2d<CTAS>(sa, &tmap_fa, fb, kb * 64, m0);
+            tma_load_2d<CTAS>(sa + A_BYTES, &tmap_fb, fb, kb * 64, n0);
           } else {
-            tma_load_2d(sa, &tmap_a, fb, kb * STAGE_K_BYTES, m0);
-            tma_load_2d(sa + A_BYTES, &tmap_b, fb, kb * STAGE_K_BYTES, n0);
+            tma_load_2d<CTAS>(sa, &tmap_a, fb, kb * STAGE_K_BYTES, m0);
+            tma_load_2d<CTAS>(sa + A_BYTES, &tmap_b, fb, kb * STAGE_K_BYTES, n0);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -319,11 +402,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
   } else if (warp == 1) {
-    // ================= MMA issuer =================
-    if (lane == 0) {
+    // ================= MMA issuer (pair leader only) =================
+    if (lane == 0 && rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long w_region = 0, w_full = 0;
+      const long long t_begin = clock64();
       auto issue = [&](int j, bool fp, int kb0, int kb1) {
         const int r = j & 1;
         const uint32_t use_parity = (uint32_t)(j >> 1) & 1u;
@@ -334,10 +419,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             // integer product of an outlier-free layer), or after this tile's drain
             const bool after_drain = HAS_FP && !fp;
             const uint32_t bar = smem_u32((after_drain ? fp_drained : acc_empty) + r);
+            const long long t0 = clock64();
             if (!mbar_wait(bar, after_drain ? use_parity : (use_parity ^ 1u), abort_flag)) { ok = false; break; }
+            w_region += clock64() - t0;
             tc_fence_after();
           }
+          const long long t1 = clock64();
           if (!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag)) { ok = false; break; }
+          w_full += clock64() - t1;
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
@@ -345,13 +434,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           for (int k = 0; k < STAGE_K_BYTES / 32; ++k) {
             // +32 bytes of K inside the swizzled row = +2 in the 16-byte start-address field
             const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-            if (fp) mma_f16(d, da + 2 * k, db + 2 * k, p.idesc_fp, accumulate);
-            else mma_i8(d, da + 2 * k, db + 2 * k, p.idesc_int, accumulate);
+            if (fp) mma_f16<CTAS>(d, da + 2 * k, db + 2 * k, p.idesc_fp, accumulate);
+            else mma_i8<CTAS>(d, da + 2 * k, db + 2 * k, p.idesc_int, accumulate);
           }
-          mma_commit(smem_u32(empty_bar + stage));          // stage reusable once these MMAs retire
+          mma_commit<CTAS>(smem_u32(empty_bar + stage));    // stage reusable once these MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          if (fp && kb == p.fp_kb - 1) mma_commit(smem_u32(fp_full + r));
-          if (!fp && kb == p.int_kb - 1) mma_commit(smem_u32(acc_full + r));
+          if (fp && kb == p.fp_kb - 1) mma_commit<CTAS>(smem_u32(fp_full + r));
+          if (!fp && kb == p.int_kb - 1) mma_commit<CTAS>(smem_u32(acc_full + r));
         }
       };
       if (HAS_FP && n_local > 0) issue(0, true, 0, p.fp_kb);
@@ -360,54 +449,84 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (HAS_FP && j + 1 < n_local) issue(j + 1, true, 0, p.fp_kb);
         issue(j, false, int_half, p.int_kb);
       }
+      if (p.dbg) {
+        unsigned long long *d = p.dbg + (size_t)blockIdx.x * 16;
+        d[0] = (unsigned long long)(clock64() - t_begin);   // MMA thread: issue loop
+        d[1] = (unsigned long long)w_region;                // ... waiting for a free accumulator region
+        d[2] = (unsigned long long)w_full;                  // ... waiting for operands
+        d[3] = (unsigned long long)n_local;
+      }
     }
   } else {
     // ================= epilogue (warps 2..9) =================
+    // Warp (sub, half) owns rows [32*sub, 32*sub+32) x columns [HALF_N*half, +HALF_N) of the tile.
     const int e = warp - 2;
     const int sub = warp & 3;                 // TMEM lane quarter this warp may read
     const int half = e >> 2;                  // which half of the tile's columns
     float *s_scol = s_vec + e * 3 * HALF_N;
     float *s_wred = s_scol + HALF_N;
     float *s_bias = s_wred + HALF_N;
+    unsigned char *s_stage = s_out + e * (EPI_BUFS * EPI_BUF_BYTES);   // staging of one 32 x 32 output chunk
     bool ok = true;
+    long long e_wait_fp = 0, e_wait_acc = 0, e_drain = 0, e_finish = 0;
+
+    // Where the outlier product of (this warp, tile) is parked inside the tile's place in `out`.
+    // Every 32 x 32 chunk is parked inside its own 32-row x 64-byte block (so the final store of one
+    // chunk never touches the parked data of another), but permuted: the jj-th 16-byte piece of lane
+    // L goes to row 8*jj + L/4, piece L%4 of the block, so one warp instruction writes 8 rows x 64
+    // contiguous bytes (whole sectors) instead of 32 rows x 16 bytes.  The same lane reads its pieces
+    // back from the same addresses; nobody else looks at them.  Sub-tiles that touch the matrix edge
+    // keep the plain row-per-lane layout with guards.
+    auto parked_piece = [&](T *sub_base, int c0, int jj) -> uint4 * {   // sub_base = &out[first row of warp][n0]
+      return reinterpret_cast<uint4 *>(sub_base + (size_t)(8 * jj + (lane >> 2)) * p.N + c0) + (lane & 3);
+    };
 
     // park T(outlier product + bias) of tile j in `out`
     auto drain = [&](int j) {
-      const int tile = blockIdx.x + j * gridDim.x;
-      const int m0 = (tile % p.num_m_tiles) * BLOCK_M;
+      const int tile = unit + j * num_units;
+      const int m0 = (tile % p.num_m_tiles) * TILE_M + rank * BLOCK_M + sub * 32;   // first row of this warp
       const int n0 = (tile / p.num_m_tiles) * BLOCK_N + half * HALF_N;
       const int r = j & 1;
       __syncwarp();
       for (int c = lane; c < HALF_N; c += 32)
         s_bias[c] = (n0 + c < p.N && p.bias) ? ldf<T>(p.bias, n0 + c) : 0.f;
       __syncwarp();
+      const long long tw = clock64();
       const bool ready = mbar_wait(smem_u32(fp_full + r), (uint32_t)(j >> 1) & 1u, abort_flag);
       if (!__all_sync(0xffffffffu, ready)) { ok = false; return; }
+      const long long tw1 = clock64();
+      e_wait_fp += tw1 - tw;
       tc_fence_after();
-      const int row = m0 + sub * 32 + lane;
+      const int row = m0 + lane;
+      const bool interior = p.vec_out && m0 + 32 <= p.M && n0 + HALF_N <= p.N;
+      T *sub_base = static_cast<T *>(p.out) + (size_t)m0 * p.N + n0;
       const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + r * BLOCK_N + half * HALF_N;
 #pragma unroll 1
       for (int c0 = 0; c0 < HALF_N; c0 += 32) {
         uint32_t f[32];
+        float o[32];
         __syncwarp();                          // tcgen05.ld is warp-collective
         tmem_ld32(taddr + c0, f);
         tmem_ld_wait();
-        const int col0 = n0 + c0;
-        if (row < p.M && col0 < p.N) {
-          float o[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(f[i]) + s_bias[c0 + i];
-          store_row32<T>(static_cast<T *>(p.out) + (size_t)row * p.N + col0, p.vec_out && col0 + 32 <= p.N,
-                         p.N - col0, o);
+        for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(f[i]) + s_bias[c0 + i];
+        if (interior) {
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) *parked_piece(sub_base, c0, jj) = pack8<T>(o + 8 * jj);
+        } else if (row < p.M && n0 + c0 < p.N) {
+          store_row32<T>(static_cast<T *>(p.out) + (size_t)row * p.N + n0 + c0, p.vec_out && n0 + c0 + 32 <= p.N,
+                         p.N - n0 - c0, o);
         }
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(fp_drained + r));
+      if (CTAS == 1) mbar_arrive(smem_u32(fp_drained + r));
+      else mbar_arrive_leader(smem_u32(fp_drained + r));
+      e_drain += clock64() - tw1;
     };
 
     auto finish = [&](int j) {
-      const int tile = blockIdx.x + j * gridDim.x;
-      const int m0 = (tile % p.num_m_tiles) * BLOCK_M;
+      const int tile = unit + j * num_units;
+      const int m0 = (tile % p.num_m_tiles) * TILE_M + rank * BLOCK_M + sub * 32;   // first row of this warp
       const int n0 = (tile / p.num_m_tiles) * BLOCK_N + half * HALF_N;
       const int r = j & 1;
       if (p.mode == 1) {
@@ -421,11 +540,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         __syncwarp();
       }
+      const int row = m0 + lane;
+      const bool row_ok = row < p.M;
+      const bool interior = p.vec_out && m0 + 32 <= p.M && n0 + HALF_N <= p.N;
+      T *sub_base = static_cast<T *>(p.out) + (size_t)m0 * p.N + n0;
+      const T *my_row = static_cast<const T *>(p.out) + (size_t)row * p.N;
+      // The parked outlier product of the first 32 columns is fetched before waiting for the integer
+      // product, the following ones one step ahead, so their L2 latency stays off the critical path.
+      uint4 pk_next[4];
+      auto prefetch_parked = [&](int c0) {
+        if (!HAS_FP || p.mode != 1) return;
+        if (interior) {
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) pk_next[jj] = *parked_piece(sub_base, c0, jj);
+        } else if (row_ok && p.vec_out && n0 + c0 + 32 <= p.N) {
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) pk_next[jj] = reinterpret_cast<const uint4 *>(my_row + n0 + c0)[jj];
+        }
+      };
+      prefetch_parked(0);
+      const long long tw = clock64();
       const bool ready = mbar_wait(smem_u32(acc_full + r), (uint32_t)(j >> 1) & 1u, abort_flag);
       if (!__all_sync(0xffffffffu, ready)) { ok = false; return; }
+      const long long tw1 = clock64();
+      e_wait_acc += tw1 - tw;
       tc_fence_after();
-      const int row = m0 + sub * 32 + lane;
-      const bool row_ok = row < p.M;
       float srow = 0.f, zs = 0.f;
       if (p.mode == 1 && row_ok) {
         srow = ldf<T>(p.row_scale, (size_t)row * p.row_stride);
@@ -436,14 +575,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll 1
       for (int c0 = 0; c0 < HALF_N; c0 += 32) {
         uint32_t v[32];
+        uint4 pk[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pk[i] = pk_next[i];
         __syncwarp();                          // tcgen05.ld is warp-collective: reconverge first
         tmem_ld32(taddr + c0, v);
+        if (c0 + 32 < HALF_N) prefetch_parked(c0 + 32);
         tmem_ld_wait();
         const int col0 = n0 + c0;
-        if (!row_ok || col0 >= p.N) continue;
+        if (col0 >= p.N) continue;             // warp-uniform
         const bool full_chunk = col0 + 32 <= p.N;
         const size_t off = (size_t)row * p.N + col0;
         if (p.mode == 0) {
+          if (!row_ok) continue;
           if (full_chunk && p.vec_out) {
             int4 *dst = reinterpret_cast<int4 *>(p.C + off);
 #pragma unroll
@@ -455,23 +599,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
           continue;
         }
-        float add[32];
+        float o[32];   // addend first, result later
         if (HAS_FP) {
-          T parked[32];
-          load_row32<T>(static_cast<const T *>(p.out) + off, full_chunk && p.vec_out, p.N - col0, parked);
+          if (interior || (row_ok && full_chunk && p.vec_out)) {
+            const T *pe = reinterpret_cast<const T *>(pk);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) add[i] = Traits<T>::to_float(parked[i]);
+            for (int i = 0; i < 32; ++i) o[i] = Traits<T>::to_float(pe[i]);
+          } else {
+            for (int i = 0; i < 32; ++i)
+              o[i] = (row_ok && col0 + i < p.N) ? Traits<T>::to_float(my_row[col0 + i]) : 0.f;
+          }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) add[i] = s_bias[c0 + i];
+          for (int i = 0; i < 32; ++i) o[i] = s_bias[c0 + i];
         }
-        if (p.y != nullptr) {
+        if (p.y != nullptr && row_ok) {
           T yv[32];
           load_row32<T>(static_cast<const T *>(p.y) + off, full_chunk && p.vec_y, p.N - col0, yv);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) add[i] += Traits<T>::to_float(yv[i]);
+          for (int i = 0; i < 32; ++i) o[i] += Traits<T>::to_float(yv[i]);
         }
-        float o[32];
 #pragma unroll
         for (int i4 = 0; i4 < 8; ++i4) {
           const float4 sc4 = reinterpret_cast<const float4 *>(s_scol + c0)[i4];
@@ -482,13 +629,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           for (int q = 0; q < 4; ++q) {
             const int i = 4 * i4 + q;
             // out = acc * (s_row * s_col) + ((zero + shift * s_row) * w_red + addend), fused multiply-adds
-            o[i] = fmaf((float)(int)v[i], srow * sc[q], fmaf(zs, wr[q], add[i]));
+            o[i] = fmaf((float)(int)v[i], srow * sc[q], fmaf(zs, wr[q], o[i]));
           }
         }
-        store_row32<T>(static_cast<T *>(p.out) + off, full_chunk && p.vec_out, p.N - col0, o);
+        if (p.vec_out) {
+          // Transpose through shared memory so that one warp instruction stores 8 rows x 64 contiguous
+          // bytes (whole sectors) instead of 32 rows x 16 bytes: lane i writes its row as four 16-byte
+          // pieces (swizzled against bank conflicts), lane L then stores piece L%4 of rows 8k + L/4.
+          __syncwarp();                        // the previous chunk has been read out of the buffer
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj)
+            *reinterpret_cast<uint4 *>(s_stage + lane * 64 + ((jj ^ ((lane >> 1) & 3)) << 4)) = pack8<T>(o + 8 * jj);
+          __syncwarp();
+          const int pc = lane & 3;
+          const bool col_ok = col0 + 8 * pc + 8 <= p.N;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int rr = 8 * k + (lane >> 2);
+            const uint4 piece = *reinterpret_cast<const uint4 *>(s_stage + rr * 64 + ((pc ^ ((rr >> 1) & 3)) << 4));
+            if (col_ok && m0 + rr < p.M)
+              *(reinterpret_cast<uint4 *>(static_cast<T *>(p.out) + (size_t)(m0 + rr) * p.N + col0) + pc) = piece;
+          }
+        } else if (row_ok) {
+          store_row32<T>(static_cast<T *>(p.out) + off, false, p.N - col0, o);
+        }
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(acc_empty + r));
+      if (CTAS == 1) mbar_arrive(smem_u32(acc_empty + r));
+      else mbar_arrive_leader(smem_u32(acc_empty + r));
+      e_finish += clock64() - tw1;
     };
 
     if (HAS_FP && n_local > 0) drain(0);
@@ -496,6 +665,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (HAS_FP && j + 1 < n_local) drain(j + 1);
       if (!ok) break;
       finish(j);
+    }
+    if (p.dbg && warp == 2 && lane == 0) {
+      unsigned long long *d = p.dbg + (size_t)blockIdx.x * 16;
+      d[4] = (unsigned long long)e_wait_fp;     // epilogue warp: waiting for an outlier product
+      d[5] = (unsigned long long)e_wait_acc;    // ... waiting for an integer product
+      d[6] = (unsigned long long)e_drain;       // ... parking outlier products
+      d[7] = (unsigned long long)e_finish;      // ... final epilogues
     }
   }
 
@@ -507,9 +683,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   }
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync_all();          // no CTA leaves while its peer may still address it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_ALLOC);
+    tmem_dealloc<CTAS>(tmem_base, TMEM_ALLOC);
   }
 }
 
@@ -535,16 +712,16 @@ EncodeTiledFn get_encode_fn() {
 
 // 2-D row-major tensor [rows, cols] of `elem_bytes` elements; box = 128 bytes of a row x box_rows.
 int make_tmap(CUtensorMap *map, const void *base, CUtensorMapDataType dt, int elem_bytes, int rows, int cols,
-              int box_rows) {
+              int box_rows, int box_row_bytes = STAGE_K_BYTES) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return QUIK_ERR_CUDA;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)cols * elem_bytes};
-  cuuint32_t box[2] = {(cuuint32_t)(STAGE_K_BYTES / elem_bytes), (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)(box_row_bytes / elem_bytes), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle sw = box_row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUresult r = fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
     return QUIK_ERR_CUDA;
@@ -552,36 +729,73 @@ int make_tmap(CUtensorMap *map, const void *base, CUtensorMapDataType dt, int el
   return QUIK_OK;
 }
 
-// tcgen05 instruction descriptor: dense, K-major A and B, M = 128.
-uint32_t make_idesc(int c_format, int ab_format, int n) {
+// tcgen05 instruction descriptor: dense, K-major A and B; m = 128 (one CTA) or 256 (CTA pair).
+uint32_t make_idesc(int c_format, int ab_format, int m, int n) {
   uint32_t d = 0;
   d |= (uint32_t)c_format << 4;      // accumulator: 1 = F32, 2 = S32
   d |= (uint32_t)ab_format << 7;     // A format
   d |= (uint32_t)ab_format << 10;    // B format
   d |= (uint32_t)(n >> 3) << 17;     // N / 8
-  d |= (uint32_t)(BLOCK_M >> 4) << 24;   // M / 16
+  d |= (uint32_t)(m >> 4) << 24;     // M / 16
   return d;
 }
 
-template <int BLOCK_N>
-constexpr size_t smem_bytes() {
-  constexpr int stages = (BLOCK_N == 256) ? 4 : 6;
-  return 1024 /*align slack*/ + (size_t)stages * (BLOCK_M + BLOCK_N) * STAGE_K_BYTES +
-         256 /*barriers, TMEM slot, abort flag*/ + 8 * 3 * (BLOCK_N / 2) * 4 /*epilogue vectors*/;
+constexpr size_t smem_bytes(int block_n, int ctas) {
+  return 1024 /*align slack*/ + (size_t)num_stages(block_n, ctas) * stage_bytes(block_n, ctas) + AUX_BYTES(block_n) +
+         8 * epi_bufs(block_n, ctas) * EPI_BUF_BYTES;
 }
 
-template <typename T, int BLOCK_N, bool HAS_FP>
+// Largest number of CTA pairs that can be resident at once (0 if pairs cannot be launched).
+template <typename Kern>
+int max_pairs(Kern kern, size_t smem) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * num_sms());
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+template <typename T, int BLOCK_N, bool HAS_FP, int CTAS>
 int launch_t(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tfa, const CUtensorMap &tfb,
              const GemmParams &p, cudaStream_t st) {
-  auto kern = gemm_tcgen05_kernel<T, BLOCK_N, HAS_FP>;
-  constexpr size_t smem = smem_bytes<BLOCK_N>();
-  static bool configured = false;   // per instantiation; the attribute is per function and idempotent
-  if (!configured) {
+  auto kern = gemm_tcgen05_kernel<T, BLOCK_N, HAS_FP, CTAS>;
+  constexpr size_t smem = smem_bytes(BLOCK_N, CTAS);
+  static int resident_units = -1;   // per instantiation: CTAs (one per SM) or CTA pairs that fit at once
+  if (resident_units < 0) {
     QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    resident_units = CTAS == 1 ? num_sms() : max_pairs(kern, smem);
   }
-  const int grid = p.num_tiles < num_sms() ? p.num_tiles : num_sms();
-  kern<<<grid, NUM_THREADS, smem, st>>>(ta, tb, tfa, tfb, p);
+  if (resident_units <= 0) return QUIK_ERR_UNSUPPORTED;
+  const int units = p.num_tiles < resident_units ? p.num_tiles : resident_units;
+  if (CTAS == 1) {
+    kern<<<units, NUM_THREADS, smem, st>>>(ta, tb, tfa, tfb, p);
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * units);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    QUIK_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, tfa, tfb, p));
+  }
   return check_launch("gemm_tcgen05_kernel");
 }
 
@@ -589,6 +803,9 @@ int launch_t(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tf
 
 void set_tile_n(int n) { g_tile_n = n; }
 int get_tile_n() { return g_tile_n; }
+void set_debug_counters(void *buf) { g_dbg = static_cast<unsigned long long *>(buf); }
+void set_cta_pair(int mode) { g_cta_pair = mode; }
+int get_cta_pair() { return g_cta_pair; }
 
 int device_status_read(int clear) {
   unsigned int v = 0;
@@ -609,10 +826,13 @@ int launch_gemm_tcgen05(const int8_t *A, const int8_t *B, int M, int N, int K, c
   const bool has_fp = ep.mode == 1 && ep.fp_a != nullptr && ep.F > 0;
   if (has_fp && (ep.F % 8 != 0 || !aligned16(ep.fp_a) || !aligned16(ep.fp_b))) return QUIK_ERR_ALIGN;
 
-  // Narrow tiles when wide ones would leave SMs idle.
-  const int m_tiles = (M + BLOCK_M - 1) / BLOCK_M;
-  const int tiles256 = m_tiles * ((N + 255) / 256);
-  int block_n = (N <= 128) ? 128 : (tiles256 >= num_sms() ? 256 : 128);
+  // CTA pairs (256-row tiles) whenever there are at least two 128-row blocks of M; narrow tiles only
+  // for narrow outputs.
+  const int ctas = (g_cta_pair == 2 || (g_cta_pair == 0 && M > BLOCK_M)) ? 2 : 1;
+  const int tile_m = BLOCK_M * ctas;
+  const int m_tiles = (M + tile_m - 1) / tile_m;
+  int block_n = (N <= 128) ? 128 : 256;
+  if (ctas == 1 && N > 128 && m_tiles * ((N + 255) / 256) < num_sms()) block_n = 128;
   if (g_tile_n == 128 || g_tile_n == 256) block_n = g_tile_n;
 
   GemmParams p{};
@@ -622,8 +842,8 @@ int launch_gemm_tcgen05(const int8_t *A, const int8_t *B, int M, int N, int K, c
   p.num_tiles = m_tiles * ((N + block_n - 1) / block_n);
   p.int_kb = (K + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
   p.fp_kb = has_fp ? (ep.F + 63) / 64 : 0;
-  p.idesc_int = make_idesc(2, 1, block_n);                              // S32 accumulate, signed 8-bit operands
-  p.idesc_fp = make_idesc(1, ep.dtype == QUIK_BF16 ? 1 : 0, block_n);   // F32 accumulate, F16 / BF16 operands
+  p.idesc_int = make_idesc(2, 1, tile_m, block_n);                              // S32 accumulate, signed 8-bit operands
+  p.idesc_fp = make_idesc(1, ep.dtype == QUIK_BF16 ? 1 : 0, tile_m, block_n);   // F32 accumulate, F16 / BF16 operands
   p.mode = ep.mode;
   p.C = ep.C;
   p.out = ep.out;
@@ -645,31 +865,37 @@ int launch_gemm_tcgen05(const int8_t *A, const int8_t *B, int M, int N, int K, c
   if (ep.mode == 0) p.vec_out = (N % 4 == 0) && aligned16(ep.C);
   else p.vec_out = (N % 8 == 0) && aligned16(ep.out);
   p.vec_y = ep.y && (N % 8 == 0) && aligned16(ep.y);
+  p.dbg = g_dbg;
 
   CUtensorMap ta, tb, tfa, tfb;
   int rc;
   if ((rc = make_tmap(&ta, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, BLOCK_M)) != QUIK_OK) return rc;
-  if ((rc = make_tmap(&tb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, block_n)) != QUIK_OK) return rc;
+  if ((rc = make_tmap(&tb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, block_n / ctas)) != QUIK_OK) return rc;
   if (has_fp) {
     const CUtensorMapDataType fdt = ep.dtype == QUIK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     if ((rc = make_tmap(&tfa, ep.fp_a, fdt, 2, M, ep.F, BLOCK_M)) != QUIK_OK) return rc;
-    if ((rc = make_tmap(&tfb, ep.fp_b, fdt, 2, N, ep.F, block_n)) != QUIK_OK) return rc;
+    if ((rc = make_tmap(&tfb, ep.fp_b, fdt, 2, N, ep.F, block_n / ctas)) != QUIK_OK) return rc;
   } else {
     tfa = ta;
     tfb = tb;
   }
-
-#define QUIK_LAUNCH(T)                                                                     \
+#define QUIK_LAUNCH_C(T, C)                                                                \
   do {                                                                                     \
     if (block_n == 256) {                                                                  \
-      return has_fp ? launch_t<T, 256, true>(ta, tb, tfa, tfb, p, st)                      \
-                    : launch_t<T, 256, false>(ta, tb, tfa, tfb, p, st);                    \
+      return has_fp ? launch_t<T, 256, true, C>(ta, tb, tfa, tfb, p, st)                   \
+                    : launch_t<T, 256, false, C>(ta, tb, tfa, tfb, p, st);                 \
     }                                                                                      \
-    return has_fp ? launch_t<T, 128, true>(ta, tb, tfa, tfb, p, st)                        \
-                  : launch_t<T, 128, false>(ta, tb, tfa, tfb, p, st);                      \
+    return has_fp ? launch_t<T, 128, true, C>(ta, tb, tfa, tfb, p, st)                     \
+                  : launch_t<T, 128, false, C>(ta, tb, tfa, tfb, p, st);                   \
+  } while (0)
+#define QUIK_LAUNCH(T)                                                                     \
+  do {                                                                                     \
+    if (ctas == 2) QUIK_LAUNCH_C(T, 2);                                                    \
+    QUIK_LAUNCH_C(T, 1);                                                                   \
   } while (0)
   if (ep.dtype == QUIK_BF16) QUIK_LAUNCH(__nv_bfloat16);
   QUIK_LAUNCH(__half);
+#undef QUIK_LAUNCH_C
 #undef QUIK_LAUNCH
 }
 

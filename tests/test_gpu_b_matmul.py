@@ -8,20 +8,24 @@ from tests.gpu_util import assert_device_clean, dev
 
 pytestmark = pytest.mark.gpu
 
-ENGINES = [("mma_sync", _lib.ENGINE_MMA_SYNC, 0), ("tcgen05_auto", _lib.ENGINE_TCGEN05, 0),
-           ("tcgen05_n128", _lib.ENGINE_TCGEN05, 128), ("tcgen05_n256", _lib.ENGINE_TCGEN05, 256)]
+# (id, engine, tile width, CTA-pair mode: 1 = single CTAs, 2 = CTA pairs)
+ENGINES = [("mma_sync", _lib.ENGINE_MMA_SYNC, 0, 0), ("tcgen05_auto", _lib.ENGINE_TCGEN05, 0, 0),
+           ("tcgen05_1cta_n128", _lib.ENGINE_TCGEN05, 128, 1), ("tcgen05_1cta_n256", _lib.ENGINE_TCGEN05, 256, 1),
+           ("tcgen05_pair_n128", _lib.ENGINE_TCGEN05, 128, 2), ("tcgen05_pair_n256", _lib.ENGINE_TCGEN05, 256, 2)]
 
 
 @pytest.fixture(params=ENGINES, ids=[e[0] for e in ENGINES])
 def engine(request):
-    _, eng, tile = request.param
+    _, eng, tile, pair = request.param
     _lib.set_engine(eng)
     _lib.set_tile_n(tile)
+    _lib.set_cta_pair(pair)
     yield request.param[0]
     torch.cuda.synchronize()
     assert_device_clean()
     _lib.set_engine(_lib.ENGINE_AUTO)
     _lib.set_tile_n(0)
+    _lib.set_cta_pair(0)
 
 
 SHAPES = [(128, 256, 128), (1, 8, 16), (3, 20, 48), (129, 260, 3840), (512, 32, 512), (300, 520, 10752),

@@ -49,6 +49,29 @@ def test_fused_forward_matches_oracle(dtype, M, K, N, F, bits):
     assert_device_clean()
 
 
+@pytest.mark.parametrize("pair", [1, 2])
+@pytest.mark.parametrize("M,K,N,F,bits", [(300, 4096, 520, 256, 4), (2048, 4096, 2048, 256, 4), (640, 11008, 512, 256, 8),
+                                          (128, 1024, 256, 64, 4), (513, 2048, 1000, 0, 4)])
+def test_fused_forward_single_cta_and_pair_agree(pair, M, K, N, F, bits):
+    """Both tile schedules (one CTA per tile, CTA pair per 256-row tile) against the oracle and each other."""
+    case = make_layer("t", M, K, N, bits, F=F, seed=7, device=dev(), clip=False)
+    _lib.set_cta_pair(pair)
+    try:
+        out = case.module(case.x.unsqueeze(0))[0]
+        torch.cuda.synchronize()
+    finally:
+        _lib.set_cta_pair(0)
+    assert_device_clean()
+    ref = _oracle_out(case, round_y=True)
+    assert rel_rms_err(out.cpu(), ref) < TOL_RMS
+    _lib.set_cta_pair(1)
+    try:
+        single = case.module(case.x.unsqueeze(0))[0]
+    finally:
+        _lib.set_cta_pair(0)
+    assert rel_rms_err(out.cpu(), single.cpu()) < 2e-3      # only the outlier product's summation order differs
+
+
 @pytest.mark.parametrize("M,bits,F", [(64, 4, 256), (5, 8, 0), (200, 8, 256)])
 def test_unfused_forward_matches_oracle(M, bits, F):
     case = make_layer("t", M, 4096, 256, bits, F=F, seed=3, device=dev(), clip=False)
