@@ -33,6 +33,7 @@ extern "C" {
 #define QUIK_ERR_SCRATCH       -7   /* scratch buffer missing or too small                      */
 #define QUIK_ERR_UNSUPPORTED   -8   /* valid for the reference, outside this build's limits     */
 #define QUIK_ERR_DEVICE_WAIT   -9   /* a bounded on-device wait ran out (reported via status)   */
+#define QUIK_ERR_TOO_LARGE    -10   /* sizes exceed the fixed scratch area of the no-allocation call */
 
 /* ---- element types of floating tensors --------------------------------------------------- */
 #define QUIK_F16   0
@@ -137,6 +138,25 @@ int quik_int8_matmul(const int8_t *A, const int8_t *B, int32_t *C, int M, int N,
 size_t quik_int4_matmul_scratch_bytes(int M, int N, int K);
 int quik_int4_matmul(const uint8_t *A, const uint8_t *B, int32_t *C, int M, int N, int K,
                      void *scratch, size_t scratch_bytes, void *stream);
+
+/* The same int4 GEMM for callers that cannot hand over scratch memory.  (It has no counterpart in the
+ * reference, whose operators allocate through torch.)  Some hosts of this library are not free to call
+ * cudaMalloc or an allocating torch routine at the moment they need the product: a serving loop that has
+ * given every free byte of the device to its own pool, or a thread that must not trigger the device-wide
+ * synchronisation an allocation can imply.  For them the widened operands are kept in a fixed array
+ * inside the library image, QUIK_NOALLOC_SCRATCH_BYTES per GPU that loads the library, held until the
+ * process exits.  The call performs no allocation and no free of any kind.
+ *   - Limit: quik_int4_matmul_scratch_bytes(M, N, K) must not exceed QUIK_NOALLOC_SCRATCH_BYTES
+ *     (e.g. (M + N) * K <= 16 Mi); larger problems return QUIK_ERR_TOO_LARGE and launch nothing.
+ *   - The first call on each device looks up the array's device address (with that device current);
+ *     make that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents; every call
+ *     rewrites the part it uses, so nothing needs clearing, but two calls that overlap in time on the
+ *     GPU (different streams) race on it.  Serialise them.
+ * Inputs, output, shapes and result are exactly those of quik_int4_matmul. */
+#define QUIK_NOALLOC_SCRATCH_BYTES (16u << 20)
+int quik_int4_matmul_fixed_scratch(const uint8_t *A, const uint8_t *B, int32_t *C, int M, int N, int K,
+                                   void *stream);
 
 /* Widen packed int4 [rows, cols/2] to int8 [rows, cols] (layout rule of include/int4.h:78-98). */
 int quik_unpack_int4(const uint8_t *src, int8_t *dst, int rows, int cols, void *stream);

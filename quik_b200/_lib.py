@@ -40,6 +40,7 @@ SIGNATURES = {
     "quik_int8_matmul": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "quik_int4_matmul_scratch_bytes": (_sz, [_i, _i, _i]),
     "quik_int4_matmul": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
+    "quik_int4_matmul_fixed_scratch": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "quik_unpack_int4": (_i, [_vp, _vp, _i, _i, _vp]),
     "quik_fused_dequantize": (_i, [_vp, _vp, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "quik_mixed_linear": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),

@@ -3,6 +3,7 @@
 // src/asymmetric/asymmetric.cu:185-196,519-524, src/matmul/matmul.cpp:8-48) as status codes.
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -57,6 +58,7 @@ const char *quik_strerror(int status) {
     case QUIK_ERR_SCRATCH: return "scratch buffer missing or too small";
     case QUIK_ERR_UNSUPPORTED: return "configuration not supported by this build";
     case QUIK_ERR_DEVICE_WAIT: return "a bounded on-device wait ran out";
+    case QUIK_ERR_TOO_LARGE: return "operands need more scratch than the library's fixed scratch area holds";
     default: return "unknown status";
   }
 }
@@ -300,6 +302,53 @@ int quik_mixed_linear(const void *q, int q_packed, const void *w, int w_packed, 
   if (bits == 8 && M <= QUIK_SMALL_M_MAX && g_small_m != 0)
     return launch_small_m(q, w, 8, M, N, K_int, ep, st);
   return run_int8_gemm(static_cast<const int8_t *>(q), static_cast<const int8_t *>(w), M, N, K_int, ep, st);
+}
+
+// ---- int4 GEMM without any caller-provided or freshly allocated scratch -----------------------
+// The widened operands live in this fixed device array.  It is part of the library image: every GPU
+// that loads the library carries these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_fixed_scratch[QUIK_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_fixed_mutex;
+void *g_fixed_ptr[64] = {};      // device address of g_fixed_scratch, looked up once per device
+
+// In host code `g_fixed_scratch` is only a handle for the runtime, not a device address; the address
+// that kernels may use has to be asked for, with the device in question current.
+int fixed_scratch_for_current_device(void **out) {
+  int dev = -1;
+  QUIK_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return QUIK_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_fixed_mutex);
+  if (g_fixed_ptr[dev] == nullptr) {
+    void *ptr = nullptr;
+    QUIK_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_fixed_scratch));
+    if (ptr == nullptr) return QUIK_ERR_CUDA;
+    g_fixed_ptr[dev] = ptr;
+  }
+  *out = g_fixed_ptr[dev];
+  return QUIK_OK;
+}
+}  // namespace
+
+int quik_int4_matmul_fixed_scratch(const uint8_t *A, const uint8_t *B, int32_t *C, int M, int N, int K,
+                                   void *stream) {
+  if (M < 0 || N < 0 || K <= 0 || K % 32 != 0) return QUIK_ERR_SHAPE;
+  if (quik_int4_matmul_scratch_bytes(M, N, K) > (size_t)QUIK_NOALLOC_SCRATCH_BYTES) return QUIK_ERR_TOO_LARGE;
+  if (M == 0 || N == 0) return QUIK_OK;
+  if (!A || !B || !C) return QUIK_ERR_NULL;
+  void *scratch = nullptr;
+  int rc = fixed_scratch_for_current_device(&scratch);
+  if (rc != QUIK_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int8_t *a8, *b8;
+  // both widened operands are rewritten in full by every call, so nothing has to be cleared first
+  rc = widen_operands(A, B, M, N, K, scratch, QUIK_NOALLOC_SCRATCH_BYTES, st, &a8, &b8);
+  if (rc != QUIK_OK) return rc;
+  Epilogue ep{};
+  ep.mode = 0;
+  ep.C = C;
+  return run_int8_gemm(a8, b8, M, N, K, ep, st);
 }
 
 }  // extern "C"
