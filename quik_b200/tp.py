@@ -35,7 +35,7 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
         if self.world == 1 or not self.gather_output:
             return out
         m, n_local = out.shape[1], out.shape[2]
-        slabs = torch.empty((self.world, m, n_local), dtype=out.dtype, device=out.device)
+        slabs = torch.empty((self.world * m, n_local), dtype=out.dtype, device=out.device)
         dist.all_gather_into_tensor(slabs, out[0].contiguous(), group=self.group)
         # [g, M, N/g] -> row-major [M, N]
-        return slabs.permute(1, 0, 2).reshape(1, m, self.world * n_local)
+        return slabs.view(self.world, m, n_local).permute(1, 0, 2).reshape(1, m, self.world * n_local)
