@@ -48,6 +48,10 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layers", default="", help="comma-separated subset of layer names")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="time eager launches instead of replaying the step as a CUDA graph")
+    ap.add_argument("--tp-mode", choices=["pull", "nccl"], default="pull",
+                    help="N > 1: assemble outputs by copy-engine pulls from symmetric memory, or by NCCL all-gather")
     return ap.parse_args()
 
 
@@ -211,7 +215,7 @@ def main():
         sl = shard_range(N, world, rank) if world > 1 else None
         c = workloads.make_layer(name, M, K, N, bits, seed=0, device=dev, n_slice=sl)
         cases.append(c)
-        layers.append(ColumnParallelMixedQLinear(c.module) if world > 1 else c.module)
+        layers.append(ColumnParallelMixedQLinear(c.module, mode=args.tp_mode) if world > 1 else c.module)
         torch.cuda.empty_cache()
     total_ops = sum(2.0 * M * N * K for (_, K, N, _) in shapes)          # whole job, all ranks
     alg_bytes = sum(c.algorithmic_bytes for c in cases)
@@ -238,6 +242,9 @@ def main():
         outs = []
         for c, layer in zip(cases, layers):
             outs.append(layer(c.x.unsqueeze(0)))
+        if world > 1:
+            for layer in layers:
+                layer.wait()          # the assembled outputs are part of the step
         return outs
 
     def sync_all():
@@ -251,20 +258,44 @@ def main():
     sync_all()
     assert _lib.device_status() == 0, "a bounded device wait ran out during warm-up"
 
+    # ---- the step as a CUDA graph: the launches (two per layer, plus the output assembly for N > 1)
+    # are replayed without host work in between; falls back to eager launches if capture fails
+    graph = None
+    if not args.no_graph:
+        try:
+            for layer in layers:
+                if hasattr(layer, "reset"):
+                    layer.reset()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                graph_outs = step()
+            graph = g
+            for _ in range(3):
+                graph.replay()
+            sync_all()
+        except Exception as exc:  # pragma: no cover - depends on the runtime
+            if rank == 0:
+                print(f"# CUDA graph capture failed, timing eager launches: {exc}", file=sys.stderr)
+            graph = None
+            sync_all()
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.25)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
-    state["on"] = True
     e0.record()
     for _ in range(args.steps):
-        step()
+        run_step()
     e1.record()
     sync_all()
-    state["on"] = False
-    clocks = sampler.stop() if rank == 0 else None
     ms_total = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([ms_total], device=dev)
@@ -272,6 +303,23 @@ def main():
         ms_total = t.item()
     ms_step = ms_total / args.steps
     value = total_ops / (ms_step * 1e-3) / 1e12
+
+    # ---- the same steps launched eagerly with CUDA events around every fused-GEMM launch (events
+    # cannot be timed inside a replayed graph); still inside the clock-sampling window
+    sync_all()
+    for layer in layers:
+        if hasattr(layer, "reset"):
+            layer.reset()             # events recorded during capture must not be waited on eagerly
+    state["on"] = True
+    ee0, ee1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ee0.record()
+    for _ in range(args.steps):
+        step()
+    ee1.record()
+    sync_all()
+    state["on"] = False
+    eager_ms_step = ee0.elapsed_time(ee1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
 
     # ---- dominant-kernel roofline (this rank's launches)
     gemm_ms, gemm_ops, per_layer = 0.0, 0.0, {}
@@ -292,6 +340,8 @@ def main():
                                f"int8 runs at twice the bf16 rate on this part; nominal dense int8 is 4500",
                 "frac_of_nominal_4500": achieved / 4500.0,
                 "per_layer_us": {k: 1e3 * sum(v) / len(v) for k, v in per_layer.items()},
+                "timing": "CUDA events around each launch of the kernel, recorded while the timed steps are "
+                          "launched eagerly right after the graph-replayed timing loop",
                 "hbm_frac_whole_step": (alg_bytes / (ms_step * 1e-3) / 1e9) / peaks["hbm_gbs"]}
 
     # ---- end to end through the public API with host buffers
@@ -308,6 +358,8 @@ def main():
             for i, layer in enumerate(layers):
                 dx[i].copy_(hx[i], non_blocking=True)
                 out = layer(dx[i].unsqueeze(0))
+                if world > 1:
+                    layer.wait()
                 ho[i].copy_(out, non_blocking=True)
 
         e_steps = max(3, min(args.steps, 10))
@@ -339,10 +391,16 @@ def main():
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": config, "roofline": roofline,
                 "cpu_baseline": cpu_base, "e2e": e2e, "gpu_launches": 2 * len(shapes) * args.steps, "clocks": clocks,
+                "launch_mode": "cuda graph replay" if graph is not None else "eager", "eager_ms_per_step": eager_ms_step,
                 "frac_of_int8_peak_whole_step": value / int8_peak}
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # leave without tearing the communicators down: graph-captured collectives and symmetric-memory
+        # handles make an orderly destroy slow or blocking on some runtimes, and the result is printed
+        sync_all()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

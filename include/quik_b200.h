@@ -194,6 +194,22 @@ int quik_mixed_linear(const void *q, int q_packed, const void *w, int w_packed,
                       const void *fp_x, const void *fp_w, const void *bias, void *out,
                       int dtype, int M, int N, int K_int, int F, int bits, void *stream);
 
+/* ==== tensor-parallel output assembly ======================================================
+ * Strided device-to-device copy (rows x width_bytes, independent pitches) issued on `stream`; runs on
+ * the copy engines.  Source or destination may be memory of a peer GPU mapped into this process
+ * (symmetric memory / IPC).  Used to pull the [M, N/g] output slabs of the other ranks into the local
+ * [M, N] result without occupying SMs.  No counterpart in the reference, which has no multi-GPU path
+ * for the layer (experiments/llama.py:295-326 places whole layers on GPUs). */
+int quik_copy_2d(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows,
+                 void *stream);
+
+/* quik_mixed_linear with a row pitch for `out` (in elements, >= N): the layer writes its N columns
+ * into a wider row-major matrix, e.g. its column range of a tensor-parallel [M, N_total] result. */
+int quik_mixed_linear_ld(const void *q, int q_packed, const void *w, int w_packed,
+                         const void *meta, const void *scale_col, const void *w_reduced,
+                         const void *fp_x, const void *fp_w, const void *bias, void *out, long long out_pitch,
+                         int dtype, int M, int N, int K_int, int F, int bits, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

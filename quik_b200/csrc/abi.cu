@@ -272,6 +272,15 @@ int quik_mixed_linear(const void *q, int q_packed, const void *w, int w_packed, 
                       const void *scale_col, const void *w_reduced, const void *fp_x, const void *fp_w,
                       const void *bias, void *out, int dtype, int M, int N, int K_int, int F, int bits,
                       void *stream) {
+  return quik_mixed_linear_ld(q, q_packed, w, w_packed, meta, scale_col, w_reduced, fp_x, fp_w, bias, out, N, dtype, M, N,
+                              K_int, F, bits, stream);
+}
+
+int quik_mixed_linear_ld(const void *q, int q_packed, const void *w, int w_packed, const void *meta,
+                         const void *scale_col, const void *w_reduced, const void *fp_x, const void *fp_w,
+                         const void *bias, void *out, long long out_pitch, int dtype, int M, int N, int K_int, int F,
+                         int bits, void *stream) {
+  if (out_pitch < N) return QUIK_ERR_SHAPE;
   if (bits != 4 && bits != 8) return QUIK_ERR_BITS;
   if (!dtype_ok(dtype)) return QUIK_ERR_DTYPE;
   if (M < 0 || N < 0 || K_int <= 0 || F < 0 || K_int % 16 != 0 || F % 8 != 0) return QUIK_ERR_SHAPE;
@@ -283,6 +292,7 @@ int quik_mixed_linear(const void *q, int q_packed, const void *w, int w_packed, 
   ep.mode = 1;
   ep.dtype = dtype;
   ep.out = out;
+  ep.ldo = out_pitch;
   ep.meta = meta;
   ep.scale_col = scale_col;
   ep.w_reduced = w_reduced;
@@ -302,6 +312,16 @@ int quik_mixed_linear(const void *q, int q_packed, const void *w, int w_packed, 
   if (bits == 8 && M <= QUIK_SMALL_M_MAX && g_small_m != 0)
     return launch_small_m(q, w, 8, M, N, K_int, ep, st);
   return run_int8_gemm(static_cast<const int8_t *>(q), static_cast<const int8_t *>(w), M, N, K_int, ep, st);
+}
+
+int quik_copy_2d(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows,
+                 void *stream) {
+  if (rows == 0 || width_bytes == 0) return QUIK_OK;
+  if (!dst || !src) return QUIK_ERR_NULL;
+  if (dst_pitch < width_bytes || src_pitch < width_bytes) return QUIK_ERR_SHAPE;
+  QUIK_CUDA_TRY(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDeviceToDevice,
+                                  static_cast<cudaStream_t>(stream)));
+  return QUIK_OK;
 }
 
 // ---- int4 GEMM without any caller-provided or freshly allocated scratch -----------------------

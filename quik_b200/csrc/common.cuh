@@ -45,12 +45,14 @@ void set_debug_counters(void *buf);    // device buffer of 16 x uint64 per CTA, 
 template <typename T> struct Traits;
 template <> struct Traits<__half> {
   using T2 = __half2;
+  static constexpr bool kIsHalf = true;
   static __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
   static __device__ __forceinline__ __half from_float(float v) { return __float2half(v); }
   static __device__ __forceinline__ int to_int_rn(__half v) { return __half2int_rn(v); }
 };
 template <> struct Traits<__nv_bfloat16> {
   using T2 = __nv_bfloat162;
+  static constexpr bool kIsHalf = false;
   static __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
   static __device__ __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
   static __device__ __forceinline__ int to_int_rn(__nv_bfloat16 v) { return __bfloat162int_rn(v); }
@@ -90,6 +92,7 @@ struct Epilogue {
   int dtype;                // QUIK_F16 / QUIK_BF16 of every floating operand
   int32_t *C;               // mode 0
   void *out;                // mode 1, [M, N]
+  long long ldo;            // row pitch of `out` in elements; 0 = N (dense)
   const void *meta;         // interleaved (scale, zero) per row, or NULL when scale_row is given
   const void *scale_row;    // [M] (fused-op form) or NULL
   const void *zero_row;     // [M] or NULL (symmetric)

@@ -136,7 +136,7 @@ gemm_mma_sync_kernel(const int8_t *__restrict__ A, const int8_t *__restrict__ B,
             if (ep.bias) add += ld_f<T>(ep.bias, col);
             if (ep.w_reduced) add = fmaf(fmaf(ep.shift_value, srow, zrow), ld_f<T>(ep.w_reduced, col), add);
             const float r = fmaf((float)v, srow * scol, add);
-            static_cast<T *>(ep.out)[off] = Traits<T>::from_float(r);
+            static_cast<T *>(ep.out)[(size_t)row * (ep.ldo > 0 ? ep.ldo : N) + col] = Traits<T>::from_float(r);
           }
         }
       }

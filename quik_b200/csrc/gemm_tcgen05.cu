@@ -65,6 +65,7 @@ struct GemmParams {
   int mode;                       // 0: int32 C, 1: dequantize
   int32_t *C;
   void *out;
+  long long ldo;                  // row pitch of `out` in elements (>= N)
   const void *row_scale;          // element (row * row_stride)
   const void *row_zero;           // may be NULL
   int row_stride;
@@ -478,7 +479,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // back from the same addresses; nobody else looks at them.  Sub-tiles that touch the matrix edge
     // keep the plain row-per-lane layout with guards.
     auto parked_piece = [&](T *sub_base, int c0, int jj) -> uint4 * {   // sub_base = &out[first row of warp][n0]
-      return reinterpret_cast<uint4 *>(sub_base + (size_t)(8 * jj + (lane >> 2)) * p.N + c0) + (lane & 3);
+      return reinterpret_cast<uint4 *>(sub_base + (size_t)(8 * jj + (lane >> 2)) * p.ldo + c0) + (lane & 3);
     };
 
     // park T(outlier product + bias) of tile j in `out`
@@ -499,7 +500,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       tc_fence_after();
       const int row = m0 + lane;
       const bool interior = p.vec_out && m0 + 32 <= p.M && n0 + HALF_N <= p.N;
-      T *sub_base = static_cast<T *>(p.out) + (size_t)m0 * p.N + n0;
+      T *sub_base = static_cast<T *>(p.out) + (size_t)m0 * p.ldo + n0;
       const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + r * BLOCK_N + half * HALF_N;
 #pragma unroll 1
       for (int c0 = 0; c0 < HALF_N; c0 += 32) {
@@ -514,7 +515,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) *parked_piece(sub_base, c0, jj) = pack8<T>(o + 8 * jj);
         } else if (row < p.M && n0 + c0 < p.N) {
-          store_row32<T>(static_cast<T *>(p.out) + (size_t)row * p.N + n0 + c0, p.vec_out && n0 + c0 + 32 <= p.N,
+          store_row32<T>(static_cast<T *>(p.out) + (size_t)row * p.ldo + n0 + c0, p.vec_out && n0 + c0 + 32 <= p.N,
                          p.N - n0 - c0, o);
         }
       }
@@ -543,8 +544,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int row = m0 + lane;
       const bool row_ok = row < p.M;
       const bool interior = p.vec_out && m0 + 32 <= p.M && n0 + HALF_N <= p.N;
-      T *sub_base = static_cast<T *>(p.out) + (size_t)m0 * p.N + n0;
-      const T *my_row = static_cast<const T *>(p.out) + (size_t)row * p.N;
+      T *sub_base = static_cast<T *>(p.out) + (size_t)m0 * p.ldo + n0;
+      const T *my_row = static_cast<const T *>(p.out) + (size_t)row * p.ldo;
       // The parked outlier product of the first 32 columns is fetched before waiting for the integer
       // product, the following ones one step ahead, so their L2 latency stays off the critical path.
       uint4 pk_next[4];
@@ -648,10 +649,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int rr = 8 * k + (lane >> 2);
             const uint4 piece = *reinterpret_cast<const uint4 *>(s_stage + rr * 64 + ((pc ^ ((rr >> 1) & 3)) << 4));
             if (col_ok && m0 + rr < p.M)
-              *(reinterpret_cast<uint4 *>(static_cast<T *>(p.out) + (size_t)(m0 + rr) * p.N + col0) + pc) = piece;
+              *(reinterpret_cast<uint4 *>(static_cast<T *>(p.out) + (size_t)(m0 + rr) * p.ldo + col0) + pc) = piece;
           }
         } else if (row_ok) {
-          store_row32<T>(static_cast<T *>(p.out) + off, false, p.N - col0, o);
+          store_row32<T>(static_cast<T *>(p.out) + (size_t)row * p.ldo + col0, false, p.N - col0, o);
         }
       }
       tc_fence_before();
@@ -847,6 +848,7 @@ int launch_gemm_tcgen05(const int8_t *A, const int8_t *B, int M, int N, int K, c
   p.mode = ep.mode;
   p.C = ep.C;
   p.out = ep.out;
+  p.ldo = ep.ldo > 0 ? ep.ldo : N;
   if (ep.meta) {
     const size_t eb = 2;
     p.row_scale = ep.meta;
@@ -863,7 +865,7 @@ int launch_gemm_tcgen05(const int8_t *A, const int8_t *B, int M, int N, int K, c
   p.y = ep.y;
   p.shift_value = ep.shift_value;
   if (ep.mode == 0) p.vec_out = (N % 4 == 0) && aligned16(ep.C);
-  else p.vec_out = (N % 8 == 0) && aligned16(ep.out);
+  else p.vec_out = (N % 8 == 0) && (p.ldo % 8 == 0) && aligned16(ep.out);
   p.vec_y = ep.y && (N % 8 == 0) && aligned16(ep.y);
   p.dbg = g_dbg;
 

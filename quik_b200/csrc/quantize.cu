@@ -31,10 +31,57 @@ __device__ __forceinline__ int quantize_code(T x, T zero, T scale) {
   return min(max(v, 0), kMaxQ) - kShift;
 }
 
+// ---- packed fp16 arithmetic for the quantizer's inner loops ---------------------------------------
+// Two gathered values travel in one 32-bit register.  Every step reproduces, per 16-bit half, exactly
+// what the scalar chain hsub -> hdiv -> half2int_rn -> clamp of the reference kernel produces:
+//   * __hsub2 rounds each half like __hsub;
+//   * __hdiv(a, b) is half(rcp.approx.ftz(b) * float(a)) plus a refinement that only touches quotients
+//     of magnitude below 2^-17, which become code 0 with or without it -- so the refinement is skipped;
+//   * clamping the quotient to [0, 2^b - 1] before rounding equals clamping after (the bounds are
+//     integers and rounding is monotone; NaN turns into 0 either way);
+//   * adding 1024 in fp16 leaves round-to-nearest-even(q) in the low mantissa bits (ulp is 1 there).
+__device__ __forceinline__ uint32_t pack_halves(uint32_t lo, uint32_t hi) { return __byte_perm(lo, hi, 0x5410); }
+
+template <int BITS>
+__device__ __forceinline__ uint32_t codes_of_pair(uint32_t pair, __half2 zero2, float rcp_scale) {
+  const __half2 d = __hsub2(*reinterpret_cast<const __half2 *>(&pair), zero2);
+  const float2 f = __half22float2(d);
+  __half2 q = __floats2half2_rn(f.x * rcp_scale, f.y * rcp_scale);
+  q = __hmin2(__hmax2(q, __float2half2_rn(0.f)), __float2half2_rn((float)((1 << BITS) - 1)));
+  q = __hadd2(q, __float2half2_rn(1024.f));
+  return *reinterpret_cast<const uint32_t *>(&q) & 0x00FF00FFu;      // code_lo | code_hi << 16, both unsigned
+}
+
+// Four pair words (8 unsigned codes) -> output bytes.  PACKED: 8 nibbles in one word (code - 8 == code ^ 8
+// on a nibble).  Otherwise one signed byte per code in two words: code - 128 == code ^ 0x80 (8 bits), and
+// code - 8 through a borrow-free byte-wise subtraction (4 bits, one code per byte).
+template <int BITS, bool PACKED>
+__device__ __forceinline__ void emit_codes(const uint32_t (&c)[4], uint32_t &w0, uint32_t &w1) {
+  if (PACKED) {
+    uint32_t w = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) w |= ((c[j] | (c[j] >> 12)) & 0xFFu) << (8 * j);
+    w0 = w ^ 0x88888888u;
+    w1 = 0;
+  } else {
+    const uint32_t a = __byte_perm(c[0], c[1], 0x6420), b = __byte_perm(c[2], c[3], 0x6420);
+    if (BITS == 8) {
+      w0 = a ^ 0x80808080u;
+      w1 = b ^ 0x80808080u;
+    } else {
+      w0 = ((a | 0x80808080u) - 0x08080808u) ^ 0x80808080u;
+      w1 = ((b | 0x80808080u) - 0x08080808u) ^ 0x80808080u;
+    }
+  }
+}
+
 // One warp per row.  IdxT: int64_t (reference ABI) or uint16_t (layer-cached ids).
 // Shared memory: [column ids of the CTA, 16-bit][one private row buffer per warp].
-template <typename T, int BITS, bool WIDE, typename IdxT>
-__global__ void __launch_bounds__(kQuantThreads)
+// CACHE != 0 (fp16 only): packed two-at-a-time arithmetic; CACHE > 0 additionally keeps the gathered
+// values of up to CACHE chunks per lane in registers between the max/min pass and the quantize pass,
+// so each value is gathered once.  CACHE == 0: scalar intrinsics (bf16).
+template <typename T, int BITS, bool WIDE, typename IdxT, int CACHE>
+__global__ void __launch_bounds__(kQuantThreads, 2)
 asym_quantize_kernel(const T *__restrict__ src, const IdxT *__restrict__ int_idx,
                      const IdxT *__restrict__ fp_idx, int rows, int cols, int num_int, int num_fp,
                      uint8_t *__restrict__ dst, T *__restrict__ meta, T *__restrict__ fp_x,
@@ -96,6 +143,92 @@ asym_quantize_kernel(const T *__restrict__ src, const IdxT *__restrict__ int_idx
     }
     __syncwarp();
 
+    uint8_t *drow = dst + (size_t)r * dst_pitch;
+    if (CACHE != 0) {
+      // ---------- fp16 fast path: packed arithmetic; CACHE > 0 also keeps the gathered pairs ----------
+      const unsigned short *row16 = reinterpret_cast<const unsigned short *>(s_row);
+      constexpr int NC = CACHE > 0 ? CACHE : 1;
+      uint32_t cache[NC][4];
+      __half2 mx2 = __float2half2_rn(-INFINITY), mn2 = __float2half2_rn(INFINITY);
+      auto gather_chunk = [&](int c, uint32_t (&pr)[4]) {
+        const uint4 idv = *reinterpret_cast<const uint4 *>(s_int + (c << 3));
+        const uint32_t w[4] = {idv.x, idv.y, idv.z, idv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pr[j] = pack_halves(row16[w[j] & 0xffffu], row16[w[j] >> 16]);
+      };
+      auto minmax_chunk = [&](const uint32_t (&pr)[4]) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          mx2 = __hmax2(mx2, *reinterpret_cast<const __half2 *>(&pr[j]));
+          mn2 = __hmin2(mn2, *reinterpret_cast<const __half2 *>(&pr[j]));
+        }
+      };
+      if (CACHE > 0) {
+#pragma unroll
+        for (int it = 0; it < NC; ++it) {
+          const int c = lane + 32 * it;
+          if (c < num_chunks) {
+            gather_chunk(c, cache[it]);
+            minmax_chunk(cache[it]);
+          }
+        }
+      } else {
+#pragma unroll 2
+        for (int c = lane; c < num_chunks; c += 32) {
+          uint32_t pr[4];
+          gather_chunk(c, pr);
+          minmax_chunk(pr);
+        }
+      }
+      float mx = warp_max(fmaxf(__low2float(mx2), __high2float(mx2)));
+      float mn = warp_min(fminf(__low2float(mn2), __high2float(mn2)));
+      const __half scale = __float2half(fmaxf((mx - mn) / (float)((1 << BITS) - 1), 1e-6f));
+      const __half zero = __float2half(mn);
+      if (lane == 0) {
+        reinterpret_cast<__half *>(meta)[2 * (size_t)r] = scale;
+        reinterpret_cast<__half *>(meta)[2 * (size_t)r + 1] = zero;
+      }
+      float rcp_scale;
+      asm("{rcp.approx.ftz.f32 %0, %1;\n}" : "=f"(rcp_scale) : "f"(__half2float(scale)));
+      const __half2 zero2 = __half2half2(zero);
+      auto emit_chunk = [&](int c, const uint32_t (&pr)[4]) {
+        uint32_t codes[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) codes[j] = codes_of_pair<BITS>(pr[j], zero2, rcp_scale);
+        uint32_t w0, w1;
+        emit_codes<BITS, (BITS == 4 && !WIDE)>(codes, w0, w1);
+        if (BITS == 4 && !WIDE) {
+          if (vec_store) {
+            *reinterpret_cast<uint32_t *>(drow + (size_t)c * 4) = w0;
+          } else {
+            const int nbytes = min(4, (num_int >> 1) - c * 4);
+            for (int j = 0; j < nbytes; ++j) drow[c * 4 + j] = (uint8_t)(w0 >> (8 * j));
+          }
+        } else {
+          if (vec_store) {
+            *reinterpret_cast<uint2 *>(drow + (size_t)c * 8) = make_uint2(w0, w1);
+          } else {
+            const int nbytes = min(8, num_int - c * 8);
+            for (int j = 0; j < nbytes; ++j)
+              drow[c * 8 + j] = (uint8_t)((j < 4 ? w0 >> (8 * j) : w1 >> (8 * (j - 4))) & 0xFF);
+          }
+        }
+      };
+      if (CACHE > 0) {
+#pragma unroll
+        for (int it = 0; it < NC; ++it) {
+          const int c = lane + 32 * it;
+          if (c < num_chunks) emit_chunk(c, cache[it]);
+        }
+      } else {
+#pragma unroll 2
+        for (int c = lane; c < num_chunks; c += 32) {
+          uint32_t pr[4];
+          gather_chunk(c, pr);
+          emit_chunk(c, pr);
+        }
+      }
+    } else {
     // ---- pass 1: max / min over the gathered integer columns
     float mx = -INFINITY, mn = INFINITY;
 #pragma unroll 2
@@ -120,7 +253,6 @@ asym_quantize_kernel(const T *__restrict__ src, const IdxT *__restrict__ int_idx
     }
 
     // ---- pass 2: quantize + pack
-    uint8_t *drow = dst + (size_t)r * dst_pitch;
 #pragma unroll 2
     for (int c = lane; c < num_chunks; c += 32) {
       const uint4 idv = *reinterpret_cast<const uint4 *>(s_int + (c << 3));
@@ -157,14 +289,16 @@ asym_quantize_kernel(const T *__restrict__ src, const IdxT *__restrict__ int_idx
       }
     }
 
+    }
+
     // ---- outlier columns, verbatim
     T *frow = fp_x + (size_t)r * num_fp;
     for (int j = lane; j < num_fp; j += 32) frow[j] = s_row[s_fp[j]];
   }
 }
 
-template <typename T, int BITS, bool WIDE, typename IdxT>
-int launch_asym_t(const void *src, int rows, int cols, const void *int_idx, int num_int,
+template <typename T, int BITS, bool WIDE, typename IdxT, int CACHE>
+int launch_asym_cached(const void *src, int rows, int cols, const void *int_idx, int num_int,
                   const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x,
                   cudaStream_t st) {
   const int int_pad = ((num_int + 7) >> 3) << 3, fp_pad = (num_fp + 7) & ~7,
@@ -177,12 +311,20 @@ int launch_asym_t(const void *src, int rows, int cols, const void *int_idx, int 
   if (warps > kQuantThreads / 32) warps = kQuantThreads / 32;
   // small rows: keep the CTA at 8 warps but do not let one CTA hog an SM's shared memory
   const size_t smem = idx_bytes + (size_t)warps * row_bytes;
-  auto kern = asym_quantize_kernel<T, BITS, WIDE, IdxT>;
-  if (smem > 48 * 1024)
-    QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  int per_sm = 1;
-  QUIK_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kQuantThreads, smem));
-  if (per_sm < 1) return QUIK_ERR_UNSUPPORTED;
+  auto kern = asym_quantize_kernel<T, BITS, WIDE, IdxT, CACHE>;
+  // attribute and occupancy are looked up once per (instantiation, shared-memory size)
+  static size_t cached_smem = 0;
+  static int cached_per_sm = 0;
+  if (cached_smem != smem || cached_per_sm < 1) {
+    if (smem > 48 * 1024)
+      QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int occ = 0;
+    QUIK_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kQuantThreads, smem));
+    if (occ < 1) return QUIK_ERR_UNSUPPORTED;
+    cached_smem = smem;
+    cached_per_sm = occ;
+  }
+  const int per_sm = cached_per_sm;
   const int grid = max(1, min(rows, num_sms() * per_sm));
   const int vec_load = (cols % 8 == 0) && aligned16(src);
   const bool packed = (BITS == 4 && !WIDE);
@@ -193,6 +335,20 @@ int launch_asym_t(const void *src, int rows, int cols, const void *int_idx, int 
       static_cast<const IdxT *>(fp_idx), rows, cols, num_int, num_fp, static_cast<uint8_t *>(dst),
       static_cast<T *>(meta), static_cast<T *>(fp_x), vec_load, vec_store, warps);
   return check_launch("asym_quantize_kernel");
+}
+
+// fp16 rows of up to 16 chunks per lane (4096 integer columns) take the register-cached packed path
+template <typename T, int BITS, bool WIDE, typename IdxT>
+int launch_asym_t(const void *src, int rows, int cols, const void *int_idx, int num_int,
+                  const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x,
+                  cudaStream_t st) {
+  constexpr bool is_half = sizeof(T) == 2 && Traits<T>::kIsHalf;
+  if (is_half && num_int <= 8 * 32 * 16)
+    return launch_asym_cached<T, BITS, WIDE, IdxT, is_half ? 16 : 0>(src, rows, cols, int_idx, num_int, fp_idx, num_fp,
+                                                                      dst, meta, fp_x, st);
+  // longer fp16 rows: same packed arithmetic, values gathered in both passes; bf16: scalar intrinsics
+  return launch_asym_cached<T, BITS, WIDE, IdxT, is_half ? -1 : 0>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
+                                                                    meta, fp_x, st);
 }
 
 template <typename T, typename IdxT>

@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(SM_THREADS)
 small_m_kernel(const uint8_t *__restrict__ q, const uint8_t *__restrict__ w, int M, int N, int row_bytes,
                const T *__restrict__ fp_x, const T *__restrict__ fp_w, int F, const T *__restrict__ meta,
                const T *__restrict__ scale_col, const T *__restrict__ wred, const T *__restrict__ bias,
-               T *__restrict__ out) {
+               T *__restrict__ out, long long ldo) {
   __shared__ int s_int[SM_WARPS][NT][32][4];
   __shared__ float s_fp[SM_WARPS][NT][32][4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -206,7 +206,7 @@ small_m_kernel(const uint8_t *__restrict__ q, const uint8_t *__restrict__ w, int
       float add = facc;
       if (bias) add += Traits<T>::to_float(bias[n]);
       add = fmaf(fmaf(shift, srow, zrow), Traits<T>::to_float(wred[n]), add);
-      out[(size_t)m * N + n] = Traits<T>::from_float(fmaf((float)acc, srow * Traits<T>::to_float(scale_col[n]), add));
+      out[(size_t)m * ldo + n] = Traits<T>::from_float(fmaf((float)acc, srow * Traits<T>::to_float(scale_col[n]), add));
     }
   }
 }
@@ -231,7 +231,7 @@ int launch_small_m(const void *q, const void *w, int bits, int M, int N, int K_i
       static_cast<const uint8_t *>(q), static_cast<const uint8_t *>(w), M, N, row_bytes,                 \
       static_cast<const T *>(ep.fp_a), static_cast<const T *>(ep.fp_b), ep.F, static_cast<const T *>(ep.meta), \
       static_cast<const T *>(ep.scale_col), static_cast<const T *>(ep.w_reduced),                         \
-      static_cast<const T *>(ep.bias), static_cast<T *>(ep.out))
+      static_cast<const T *>(ep.bias), static_cast<T *>(ep.out), ep.ldo > 0 ? ep.ldo : (long long)N)
 #define QUIK_SM_NT(T, B)                                                                                  \
   do {                                                                                                    \
     if (nt == 4) QUIK_SM(T, B, 4);                                                                        \

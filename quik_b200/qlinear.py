@@ -65,6 +65,9 @@ class MixedQLinear(torch.nn.Module):
     # optional profiling hook: called as hook(module, begin: bool) right before / after the fused
     # GEMM launch (on the launching stream), e.g. to record CUDA events
     launch_hook = None
+    # optional caller-owned output buffer [M, out_features] (e.g. symmetric memory of a tensor-parallel
+    # group); used by the fused path when its shape, dtype and device match
+    out_buffer = None
 
     def __init__(self, in_features, out_features, shared_input=None,
                  fp_features_num=0, symm=False, bits=4, dtype=torch.float16):
@@ -142,15 +145,20 @@ class MixedQLinear(torch.nn.Module):
         N = self.out_features
         hook = MixedQLinear.launch_hook
         with torch.cuda.device(x.device):
-            out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+            ob = self.out_buffer
+            if ob is not None and tuple(ob.shape) == (M, N) and ob.dtype == x.dtype and ob.device == x.device \
+                    and ob.stride(1) == 1 and ob.stride(0) >= N:
+                out = ob                         # may be a column range of a wider row-major matrix
+            else:
+                out = torch.empty((M, N), dtype=x.dtype, device=x.device)
             F = self.fp_features_num
             if hook is not None:
                 hook(self, True)
-            check(load().quik_mixed_linear(
+            check(load().quik_mixed_linear_ld(
                 ptr(q), int(packed), ptr(w), int(packed), ptr(shared_input.meta), ptr(self.weights_scales),
                 ptr(self.reduced_w), ptr(shared_input.fp_x) if F > 0 else None,
                 ptr(self.fp_weight) if F > 0 else None, ptr(self.bias) if self.bias is not None else None,
-                ptr(out), dtype_code(x.dtype), M, N, self.int_features_num, F, self.bits, stream_of(x)),
+                ptr(out), out.stride(0), dtype_code(x.dtype), M, N, self.int_features_num, F, self.bits, stream_of(x)),
                 "MixedQLinear.forward")
             if hook is not None:
                 hook(self, False)

@@ -2,9 +2,21 @@
 
 The layer shards naturally by output channel: rank r holds rows [r*N/g, (r+1)*N/g) of int_weight,
 fp_weight, weights_scales and reduced_w; the activations are replicated and every rank runs the
-(cheap) quantizer itself, so no broadcast sits on the critical path.  The only exchange is one
-all-gather of the M x N/g output slabs (NCCL over NVLink); the reference has no multi-GPU path
-for the layer (experiments/llama.py:295-326 only places whole layers on different GPUs).
+(cheap) quantizer itself, so no broadcast sits on the critical path.  The only exchange is the
+assembly of the [M, N] output from the g slabs [M, N/g].  The reference has no multi-GPU path for
+the layer (experiments/llama.py:295-326 only places whole layers on different GPUs).
+
+Two ways to assemble:
+
+``mode="pull"`` (default on NVLink machines): the row-major [M, N] result of every rank lives in
+symmetric memory and the rank's fused kernel writes its own column range into it in place (output
+row pitch N).  After a stream-ordered barrier each rank pulls the g-1 remote column ranges from the
+peers' buffers into the same ranges of its own with strided copies on the copy engines
+(``quik_copy_2d``) on a side stream.  No SM time, no staging buffer, no permute pass, no local copy,
+and the transfer of layer i overlaps the kernels of layer i+1.
+
+``mode="nccl"``: ``all_gather_into_tensor`` of the slabs followed by a permute to row-major (also
+the path used on CPU/gloo in the tests).
 """
 from __future__ import annotations
 
@@ -21,19 +33,87 @@ def shard_range(n_total: int, world: int, rank: int, multiple: int = 8) -> slice
 
 
 class ColumnParallelMixedQLinear(torch.nn.Module):
-    """Wraps the local shard (a MixedQLinear over N/g output channels) and assembles the full output."""
+    """Wraps the local shard (a MixedQLinear over N/g output channels) and assembles the full output.
 
-    def __init__(self, local: torch.nn.Module, group=None, gather_output: bool = True):
+    ``forward`` returns the [1, M, N] result; in pull mode the tensor is complete once ``wait()`` has
+    been called (or the side stream has been joined by other means) -- the copies run on ``comm_stream``.
+    """
+
+    def __init__(self, local: torch.nn.Module, group=None, gather_output: bool = True, mode: str = "nccl",
+                 comm_stream=None):
         super().__init__()
         self.local = local
-        self.group = group
+        self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
         self.gather_output = gather_output
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
+        self.mode = mode
+        self.comm_stream = comm_stream
+        self._slab = None          # symmetric [M, N/g]
+        self._hdl = None
+        self._full = None          # local [M, N]
+        self._done = None          # event: assembly of the last forward finished
 
+    # ---- pull mode ---------------------------------------------------------------------------
+    def _setup_pull(self, m, n_local, dtype, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        n = n_local * self.world
+        # the whole [M, N] result lives in symmetric memory; the local fused kernel writes its column
+        # range in place (row pitch N), the peers read that range from here
+        self._full = symm_mem.empty((m, n), dtype=dtype, device=device)
+        self._hdl = symm_mem.rendezvous(self._full, self.group)
+        self._slab = self._full[:, self.rank * n_local:(self.rank + 1) * n_local]
+        self.local.out_buffer = self._slab
+        if self.comm_stream is None:
+            self.comm_stream = torch.cuda.Stream(device=device)
+
+    def _forward_pull(self, x):
+        from ._lib import check, load
+        m = x.shape[-2]
+        n_local = self.local.out_features
+        if self._full is None or self._full.shape[0] != m:
+            self._setup_pull(m, n_local, x.dtype, x.device)
+        cur = torch.cuda.current_stream(x.device)
+        if self._done is not None:
+            cur.wait_event(self._done)          # peers have finished reading the previous contents
+        out = self.local(x)                      # writes its column range of self._full
+        assert out.data_ptr() == self._slab.data_ptr(), "local layer did not write into the symmetric buffer"
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        lib = load()
+        es = self._full.element_size()
+        width = n_local * es
+        pitch = self._full.shape[1] * es
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ready)
+            self._hdl.barrier(channel=0)         # every rank's column range of this layer is complete
+            for step in range(1, self.world):
+                peer = (self.rank + step) % self.world      # walk the ring so the links load evenly
+                src = self._hdl.get_buffer(peer, tuple(self._full.shape), self._full.dtype)
+                off = peer * width
+                check(lib.quik_copy_2d(self._full.data_ptr() + off, pitch, src.data_ptr() + off, pitch, width, m,
+                                       self.comm_stream.cuda_stream), "quik_copy_2d")
+            self._hdl.barrier(channel=1)         # nobody still reads a range when it is overwritten next time
+            self._done = torch.cuda.Event()
+            self._done.record(self.comm_stream)
+        return self._full.unsqueeze(0)
+
+    def reset(self):
+        """Forget the completion event of earlier forwards (call before capturing a CUDA graph)."""
+        self._done = None
+
+    def wait(self):
+        """Make the current stream wait for the assembly of the last forward."""
+        if self._done is not None:
+            torch.cuda.current_stream().wait_event(self._done)
+
+    # ---- forward -----------------------------------------------------------------------------
     def forward(self, x):
-        out = self.local(x)                                  # [1, M, N/g]
         if self.world == 1 or not self.gather_output:
-            return out
+            return self.local(x)
+        if self.mode == "pull":
+            return self._forward_pull(x)
+        out = self.local(x)                                  # [1, M, N/g]
         m, n_local = out.shape[1], out.shape[2]
         slabs = torch.empty((self.world * m, n_local), dtype=out.dtype, device=out.device)
         dist.all_gather_into_tensor(slabs, out[0].contiguous(), group=self.group)

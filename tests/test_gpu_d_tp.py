@@ -1,0 +1,55 @@
+"""GPU, 2 ranks (skipped with fewer than 2 GPUs): the tensor-parallel layer assembles the same [M, N]
+output as the single-GPU layer, with both assembly paths (copy-engine pulls, NCCL all-gather)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from quik_b200.tp import ColumnParallelMixedQLinear, shard_range
+        from quik_b200.workloads import make_layer
+        M, K, N = 256, 1024, 1024
+        full = make_layer("f", M, K, N, 4, F=64, seed=3, device=dev, clip=False)
+        want = full.module(full.x.unsqueeze(0))
+        res = {}
+        for mode in ("nccl", "pull"):
+            shard = make_layer("s", M, K, N, 4, F=64, seed=3, device=dev, clip=False, n_slice=shard_range(N, world, rank))
+            layer = ColumnParallelMixedQLinear(shard.module, mode=mode)
+            for _ in range(3):                      # repeated calls reuse the slab
+                got = layer(shard.x.unsqueeze(0))
+                if mode == "pull":
+                    layer.wait()
+                torch.cuda.synchronize()
+            res[mode] = bool(torch.equal(got, want))
+        q.put((rank, res))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_two_ranks():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    results = dict(q.get(timeout=10) for _ in range(2))
+    assert results == {0: {"nccl": True, "pull": True}, 1: {"nccl": True, "pull": True}}
