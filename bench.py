@@ -32,6 +32,9 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 
 METRIC = "MixedQLinear TOPS (Llama-2 linear shapes, fused quantize+GEMM+dequant)"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_tcgen05_kernel at M = 2048, F = 256, from one
+# `ncu --set full` capture of a bench step (profiles/gemm_tcgen05_llama7b_m2048.md); key = (K, N)
+NCU_TRAFFIC_BYTES_M2048 = {(4096, 12288): 84.55e6, (4096, 4096): 26.88e6, (4096, 22016): 178.77e6, (11008, 4096): 84.54e6}
 CPU_SAMPLE_TOKENS = 256
 
 
@@ -333,8 +336,15 @@ def main():
     peaks = load_peaks()
     int8_peak = 2.0 * peaks["bf16_tflops"]
     achieved = gemm_ops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    traffic = None
+    if world == 1 and M == 2048 and args.model == "7b" and used:
+        per = [NCU_TRAFFIC_BYTES_M2048.get((mod.in_features, mod.out_features)) for _, mod in used]
+        if all(v is not None for v in per):
+            traffic = sum(per) / len(per)          # bytes per launch, averaged over the timed launches
     roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
-                "frac": achieved / int8_peak if int8_peak else None, "traffic": None,
+                "frac": achieved / int8_peak if int8_peak else None, "traffic": traffic,
+                "algorithmic_bytes_per_launch": sum(c.M * (c.K - c.F) + c.N * (c.K - c.F) + 2 * c.F * (c.M + c.N)
+                                                    + 2 * c.M * c.N for c in cases) / len(cases),
                 "kernel": "gemm_tcgen05_kernel (fused int8 GEMM + fp16 outlier GEMM + dequantize)",
                 "peak_source": f"2 x bf16 dense GEMM peak of {peaks['source']} ({peaks['bf16_tflops']} TF/s burst); "
                                f"int8 runs at twice the bf16 rate on this part; nominal dense int8 is 4500",
