@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layers", default="", help="comma-separated subset of layer names")
+    ap.add_argument("--no-block", action="store_true",
+                    help="skip the decoder-block prefill measurement (BASELINE config 2) that rides along at N=1")
     ap.add_argument("--no-graph", action="store_true",
                     help="time eager launches instead of replaying the step as a CUDA graph")
     ap.add_argument("--tp-mode", choices=["pull", "nccl"], default="pull",
@@ -391,6 +393,34 @@ def main():
                "d2h_bytes_per_step": d2h, "ms_per_step": ms / e_steps, "steps": e_steps}
     assert _lib.device_status() == 0, "a bounded device wait ran out"
 
+    # ---- BASELINE config 2 rides along: one Llama-2-7B-shaped decoder block, prefill of 2048 tokens
+    block = None
+    if world == 1 and not args.no_block and args.model == "7b" and M == 2048:
+        try:
+            from quik_b200.block import QuikLlamaBlock
+            MixedQLinear.launch_hook = None
+            del cases, layers
+            torch.cuda.empty_cache()
+            blk = QuikLlamaBlock(4096, 32, 11008, seed=0, device=dev)
+            xb = torch.randn(1, 2048, 4096, generator=torch.Generator().manual_seed(0)).half().to(dev)
+            for _ in range(3):
+                blk(xb)
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(10):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                blk(xb)
+                b.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(b))
+            med = statistics.median(ts)
+            block = {"workload": "one Llama-2-7B decoder block (hidden 4096, 32 heads, intermediate 11008, RMSNorm, RoPE, "
+                                 "SDPA), all 7 linears MixedQLinear (down int8), batch 1 x 2048 tokens, eager launches",
+                     "ms": med, "prefill_tokens_per_s_per_block": 2048 / (med * 1e-3)}
+        except Exception as exc:  # pragma: no cover
+            block = {"error": str(exc)[:200]}
+
     cpu_base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu_base = cpu_fake_quant_baseline(shapes, CPU_SAMPLE_TOKENS, 5, 1)
@@ -402,6 +432,7 @@ def main():
                 "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": config, "roofline": roofline,
                 "cpu_baseline": cpu_base, "e2e": e2e, "gpu_launches": 2 * len(shapes) * args.steps, "clocks": clocks,
                 "launch_mode": "cuda graph replay" if graph is not None else "eager", "eager_ms_per_step": eager_ms_step,
+                "decoder_block": block,
                 "frac_of_int8_peak_whole_step": value / int8_peak}
         print(json.dumps(line), flush=True)
     if world > 1:

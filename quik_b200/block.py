@@ -1,0 +1,110 @@
+"""One Llama-2-style decoder block whose seven linear layers are MixedQLinear modules, wired the way the
+reference wires them (QUIK experiments/llama.py:394-440): q/k/v share one quantized input (group of 3),
+gate/up share one (group of 2), o and down quantize on their own; down_proj may run in 8 bits
+(``int8_down_proj``).  RMSNorm, rotary embedding and attention are plain torch (``F.scaled_dot_product_attention``);
+they are the callers on either side of the hot path, not part of it.  Weights are random (seeded) and
+quantized per output channel by symmetric round-to-nearest with clipping search, outlier columns are seed-chosen.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from .qlinear import MixedQLinear, SharedQuantizedInput
+from .workloads import rtn_clip_scales
+
+
+class QuikLlamaBlock(torch.nn.Module):
+    def __init__(self, hidden=4096, heads=32, intermediate=11008, kv_heads=None, bits=4, down_bits=8,
+                 fp_features=256, seed=0, device="cuda", dtype=torch.float16, eps=1e-5, rope_theta=10000.0,
+                 clip=True, keep_dense=False):
+        super().__init__()
+        kv_heads = kv_heads or heads
+        self.hidden, self.heads, self.kv_heads, self.head_dim = hidden, heads, kv_heads, hidden // heads
+        self.eps, self.rope_theta = eps, rope_theta
+        g = torch.Generator().manual_seed(seed)
+        kv_dim = self.head_dim * kv_heads
+        # shared quantized inputs, in the reference's call order [k, v, q] and [up, gate]
+        self.qkv_shared = SharedQuantizedInput(3)
+        self.mlp_shared = SharedQuantizedInput(2)
+        dense = {}
+        # the members of a group must agree on the outlier columns (the cached quantized input is shared):
+        # each member draws them from a generator seeded per group
+        mods = {}
+        for name, out_f in (("k_proj", kv_dim), ("v_proj", kv_dim), ("q_proj", hidden)):
+            perm_gen = torch.Generator().manual_seed(seed + 1)
+            mods[name], dense[name] = self._member(hidden, out_f, bits, fp_features, perm_gen, g, device, dtype,
+                                                   self.qkv_shared, clip)
+        for name, out_f in (("up_proj", intermediate), ("gate_proj", intermediate)):
+            perm_gen = torch.Generator().manual_seed(seed + 2)
+            mods[name], dense[name] = self._member(hidden, out_f, bits, fp_features, perm_gen, g, device, dtype,
+                                                   self.mlp_shared, clip)
+        perm_gen = torch.Generator().manual_seed(seed + 3)
+        mods["o_proj"], dense["o_proj"] = self._member(hidden, hidden, bits, fp_features, perm_gen, g, device, dtype, None, clip)
+        perm_gen = torch.Generator().manual_seed(seed + 4)
+        mods["down_proj"], dense["down_proj"] = self._member(intermediate, hidden, down_bits, fp_features, perm_gen, g,
+                                                             device, dtype, None, clip)
+        for k, v in mods.items():
+            setattr(self, k, v)
+        self.dense = dense if keep_dense else None       # fake-quantized fp weights, for reference checks
+        self.input_norm = torch.nn.Parameter(torch.ones(hidden, dtype=dtype, device=device), requires_grad=False)
+        self.post_norm = torch.nn.Parameter(torch.ones(hidden, dtype=dtype, device=device), requires_grad=False)
+
+    @staticmethod
+    def _member(in_f, out_f, bits, fp_features, perm_gen, wgen, device, dtype, shared, clip):
+        w = (0.02 * torch.randn(out_f, in_f, generator=wgen)).to(dtype).to(device)
+        fp_idx = torch.sort(torch.randperm(in_f, generator=perm_gen)[:fp_features])[0] if fp_features > 0 else None
+        mask = torch.ones(in_f, dtype=torch.bool)
+        if fp_idx is not None:
+            mask[fp_idx] = False
+        int_cols = torch.arange(in_f)[mask].to(device)
+        scales = rtn_clip_scales(w[:, int_cols], bits, clip=clip)
+        lo, hi = (-8, 7) if bits == 4 else (-128, 127)
+        w_rtn = w.clone()
+        w_rtn[:, int_cols] = (scales * torch.clamp(torch.round(w[:, int_cols].float() / scales), lo, hi)).to(dtype)
+        lin = torch.nn.Linear(in_f, out_f, bias=False)
+        mod = MixedQLinear.from_float(lin, w_rtn, scales, shared_input=shared, fp_indices=fp_idx, bits=bits).to(device)
+        return mod, w_rtn
+
+    # ---- the non-linear glue (plain torch) ----------------------------------------------------
+    def _rms_norm(self, x, weight):
+        v = x.float()
+        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)
+        return (v.to(x.dtype)) * weight
+
+    def _rope(self, q, k):
+        s = q.shape[-2]
+        inv = 1.0 / (self.rope_theta ** (torch.arange(0, self.head_dim, 2, device=q.device).float() / self.head_dim))
+        ang = torch.outer(torch.arange(s, device=q.device).float(), inv)
+        cos, sin = torch.cat([ang.cos(), ang.cos()], -1).to(q.dtype), torch.cat([ang.sin(), ang.sin()], -1).to(q.dtype)
+
+        def rot(t):
+            h = t.shape[-1] // 2
+            return torch.cat([-t[..., h:], t[..., :h]], -1)
+        return q * cos + rot(q) * sin, k * cos + rot(k) * sin
+
+    def forward(self, x, linear=None):
+        """x: [1, S, hidden].  ``linear(name, x)`` may replace the quantized layers (reference checks)."""
+        lin = linear or (lambda name, t: getattr(self, name)(t))
+        b, s, _ = x.shape
+        h = self._rms_norm(x, self.input_norm)
+        k = lin("k_proj", h)
+        v = lin("v_proj", h)
+        q = lin("q_proj", h)
+        q = q.view(b, s, self.heads, self.head_dim).transpose(1, 2)
+        k = k.view(b, s, self.kv_heads, self.head_dim).transpose(1, 2)
+        v = v.view(b, s, self.kv_heads, self.head_dim).transpose(1, 2)
+        q, k = self._rope(q, k)
+        if self.kv_heads != self.heads:
+            rep = self.heads // self.kv_heads
+            k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=1.0 / math.sqrt(self.head_dim))
+        a = a.transpose(1, 2).reshape(b, s, self.hidden)
+        x = x + lin("o_proj", a)
+        h = self._rms_norm(x, self.post_norm)
+        up = lin("up_proj", h)
+        gate = lin("gate_proj", h)
+        x = x + lin("down_proj", F.silu(gate) * up)
+        return x
