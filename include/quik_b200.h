@@ -46,7 +46,9 @@ extern "C" {
 #define QUIK_ENGINE_MMA_SYNC   2
 /* Output-tile width of the tcgen05 engine: 0 = chosen by shape, 128 or 256. */
 #define QUIK_CFG_TILE_N        2
-/* 1 (default): int8 layers with M <= QUIK_SMALL_M_MAX use the weight-streaming engine; 0: never. */
+/* int8 layers with M <= QUIK_SMALL_M_MAX tokens: 1 (default) weight streaming, engine chosen by the size of the
+ * weights; 2 weight streaming on mma.sync; 3 weight streaming on tcgen05; 0 the tensor-core GEMM.
+ * (4-bit layers choose by the operand layout, see quik_mixed_linear.) */
 #define QUIK_CFG_SMALL_M       3
 /* CTA pairs (cta_group::2, 256-row tiles) in the tcgen05 engine: 0 = when M > 128, 1 = never, 2 = always. */
 #define QUIK_CFG_CTA_PAIR      4
@@ -186,8 +188,12 @@ int quik_fused_dequantize(const void *A, const void *B, int bits,
  *   meta     [2*M] dtype (scale, zero) per row;  scale_col, w_reduced [N] dtype
  *   fp_x     [M, F] dtype, fp_w [N, F] dtype (F may be 0: both NULL);  bias [N] dtype or NULL
  *   out      [M, N] dtype
- * Packed operands are accepted by the weight-streaming engine (M <= QUIK_SMALL_M_MAX);
- * one-code-per-byte operands by the tensor-core engine.  K_int % 16 == 0, F % 8 == 0. */
+ * 4-bit layers choose the engine by the operand layout:
+ *   q one per byte, w one per byte   tensor-core GEMM (any M);
+ *   q one per byte, w packed         weight streaming on tcgen05 (M <= QUIK_SMALL_M_MAX, K_int % 32 == 0): the
+ *                                    packed weights are widened on chip on their way to the tensor cores;
+ *   q packed,       w packed         weight streaming on mma.sync (M <= QUIK_SMALL_M_MAX, K_int % 32 == 0).
+ * K_int % 16 == 0, F % 8 == 0. */
 #define QUIK_SMALL_M_MAX 16
 int quik_mixed_linear(const void *q, int q_packed, const void *w, int w_packed,
                       const void *meta, const void *scale_col, const void *w_reduced,

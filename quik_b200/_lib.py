@@ -122,8 +122,18 @@ def set_cta_pair(mode: int) -> None:
     check(load().quik_config_set(CFG_CTA_PAIR, mode), "quik_config_set")
 
 
-def set_small_m(on: bool) -> None:
-    check(load().quik_config_set(CFG_SMALL_M, int(on)), "quik_config_set")
+SMALL_M_OFF, SMALL_M_AUTO, SMALL_M_MMA_SYNC, SMALL_M_TCGEN05 = 0, 1, 2, 3
+small_m_mode = SMALL_M_AUTO      # mirror of QUIK_CFG_SMALL_M, read by MixedQLinear on every call
+
+
+def set_small_m(mode) -> None:
+    """Engine for layers with at most SMALL_M_MAX tokens: 0 = none (tensor-core GEMM on widened weights),
+    1 / True = weight streaming, engine by layer (4-bit: mma.sync; 8-bit: by weight size), 2 = weight
+    streaming on mma.sync, 3 = weight streaming on tcgen05."""
+    global small_m_mode
+    mode = int(mode)
+    check(load().quik_config_set(CFG_SMALL_M, mode), "quik_config_set")
+    small_m_mode = mode
 
 
 def device_status(clear: bool = True) -> int:

@@ -77,7 +77,8 @@ int quik_config_set(int key, int value) {
     return QUIK_OK;
   }
   if (key == QUIK_CFG_SMALL_M) {
-    g_small_m = value ? 1 : 0;
+    if (value < 0 || value > 3) return QUIK_ERR_UNSUPPORTED;
+    g_small_m = value;
     return QUIK_OK;
   }
   if (key == QUIK_CFG_CTA_PAIR) {
@@ -301,16 +302,20 @@ int quik_mixed_linear_ld(const void *q, int q_packed, const void *w, int w_packe
   ep.fp_a = F > 0 ? fp_x : nullptr;
   ep.fp_b = F > 0 ? fp_w : nullptr;
   ep.F = F;
-  const bool packed4 = bits == 4 && (q_packed || w_packed);
-  if (packed4) {
-    // packed int4 operands: weight-streaming engine; both operands must be packed
-    if (!(q_packed && w_packed)) return QUIK_ERR_UNSUPPORTED;
+  if (bits == 4 && (q_packed || w_packed)) {
+    // packed int4 weights: weight-streaming engines (few tokens only)
+    if (!w_packed) return QUIK_ERR_UNSUPPORTED;
     if (K_int % 32 != 0) return QUIK_ERR_SHAPE;
-    return launch_small_m(q, w, 4, M, N, K_int, ep, st);
+    if (q_packed) return launch_small_m(q, w, 4, M, N, K_int, ep, st);      // mma.sync, both operands packed
+    return launch_stream_w(q, w, 4, M, N, K_int, ep, st);                   // tcgen05, token codes one per byte
   }
-  // one code per byte: int8 layers with few tokens also stream their weights
-  if (bits == 8 && M <= QUIK_SMALL_M_MAX && g_small_m != 0)
-    return launch_small_m(q, w, 8, M, N, K_int, ep, st);
+  // one code per byte: int8 layers with few tokens also stream their weights.  In automatic mode the tcgen05
+  // engine takes the large layers (it holds 0.85 of the HBM rate there, the mma.sync engine 0.58) and the
+  // mma.sync engine the small ones, where its shorter start-up counts for more.
+  if (bits == 8 && M <= QUIK_SMALL_M_MAX && g_small_m != 0) {
+    const bool tc = g_small_m == 3 || (g_small_m == 1 && (size_t)N * (size_t)K_int >= ((size_t)64 << 20));
+    return tc ? launch_stream_w(q, w, 8, M, N, K_int, ep, st) : launch_small_m(q, w, 8, M, N, K_int, ep, st);
+  }
   return run_int8_gemm(static_cast<const int8_t *>(q), static_cast<const int8_t *>(w), M, N, K_int, ep, st);
 }
 

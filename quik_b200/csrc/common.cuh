@@ -40,6 +40,7 @@ int get_tile_n();
 void set_cta_pair(int mode);           // 0 = by shape, 1 = never, 2 = always
 int get_cta_pair();
 void set_debug_counters(void *buf);    // device buffer of 16 x uint64 per CTA, or NULL
+unsigned long long *get_debug_counters();
 
 // ---- dtype traits ---------------------------------------------------------------------------
 template <typename T> struct Traits;
@@ -112,5 +113,8 @@ int launch_gemm_mma_sync(const int8_t *A, const int8_t *B, int M, int N, int K, 
                          cudaStream_t st);
 int launch_small_m(const void *q, const void *w, int bits, int M, int N, int K_int,
                    const Epilogue &ep, cudaStream_t st);
+// tcgen05 weight streaming (stream_w.cu): q one code per byte, w packed int4 (bits 4) or int8 (bits 8)
+int launch_stream_w(const void *q, const void *w, int bits, int M, int N, int K_int, const Epilogue &ep,
+                    cudaStream_t st);
 
 }  // namespace quik

@@ -1,17 +1,16 @@
 // Activation quantizers.
 //
-// asym_quantize_kernel: per-token asymmetric int4/int8 quantizer with outlier-column gather.
+// asym_quantize_row_kernel: per-token asymmetric int4/int8 quantizer with outlier-column gather.
 // Semantics follow the reference kernel (QUIK src/asymmetric/asymmetric.cu:340-490): per row,
 // max/min over the gathered integer columns, scale = T(fmaxf((max-min)/(2^b-1), 1e-6f)), zero =
 // min, code = clamp(rn(hdiv(hsub(x, zero), scale)), 0, 2^b-1) - 2^(b-1), outlier columns copied.
 //
 // Design for B200: the reference reads every row three times through 8-byte indices with 2-byte
-// loads, one 1024-thread block per row and block-wide barriers.  Here a CTA keeps the column ids
-// in shared memory as 16-bit values for its whole lifetime and every warp owns whole rows: it
-// streams a row from HBM exactly once (16-byte cp.async into its private shared-memory buffer)
-// and does min/max (warp shuffles only), quantize+pack and the outlier gather from that copy, so
-// no block-wide barrier sits on the row loop.  HBM traffic per row: cols*2 bytes in, codes +
-// outliers + meta out.
+// loads, one 1024-thread block per row.  Here a row is read from HBM exactly once (16-byte cp.async
+// into shared memory, the next row already in flight), the column ids are 16-bit and live in
+// registers for the CTA's lifetime, each value is gathered once and kept in registers between the
+// max/min pass and the quantize pass, and fp16 rows are processed two values per instruction.
+// HBM traffic per row: cols*2 bytes in, codes + outliers + meta out.
 #include "common.cuh"
 
 namespace quik {
@@ -75,243 +74,213 @@ __device__ __forceinline__ void emit_codes(const uint32_t (&c)[4], uint32_t &w0,
   }
 }
 
-// One warp per row.  IdxT: int64_t (reference ABI) or uint16_t (layer-cached ids).
-// Shared memory: [column ids of the CTA, 16-bit][one private row buffer per warp].
-// CACHE != 0 (fp16 only): packed two-at-a-time arithmetic; CACHE > 0 additionally keeps the gathered
-// values of up to CACHE chunks per lane in registers between the max/min pass and the quantize pass,
-// so each value is gathered once.  CACHE == 0: scalar intrinsics (bf16).
-template <typename T, int BITS, bool WIDE, typename IdxT, int CACHE>
-__global__ void __launch_bounds__(kQuantThreads, 2)
-asym_quantize_kernel(const T *__restrict__ src, const IdxT *__restrict__ int_idx,
-                     const IdxT *__restrict__ fp_idx, int rows, int cols, int num_int, int num_fp,
-                     uint8_t *__restrict__ dst, T *__restrict__ meta, T *__restrict__ fp_x,
-                     int vec_load, int vec_store, int warps_per_cta) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int num_chunks = (num_int + 7) >> 3;           // 8 codes per chunk
-  const int int_pad = num_chunks << 3;
-  const int fp_pad = (num_fp + 7) & ~7;
-  const int cols_pad = (cols + 7) & ~7;
-  uint16_t *s_int = reinterpret_cast<uint16_t *>(smem_raw);               // [int_pad]
-  uint16_t *s_fp = s_int + int_pad;                                       // [fp_pad]
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  T *s_row = reinterpret_cast<T *>(s_fp + fp_pad) + (size_t)warp * cols_pad;   // this warp's row
+// ---- one CTA per row at a time ------------------------------------------------------------------------
+// 256 threads share a row: each thread gathers a few chunks of 8 values (kept in registers between the
+// max/min pass and the quantize pass), the row's max/min go through one block-wide reduction.  A CTA walks
+// over rows blockIdx.x, blockIdx.x + gridDim.x, ...; the column ids are read once per CTA (16-bit, in
+// registers) and the next row is copied into the second shared-memory buffer (16-byte cp.async) while the
+// current one is processed, so HBM latency is paid once per CTA, not once per row.
+// IdxT: int64_t (reference ABI) or uint16_t (layer-cached ids).
+// NC = register-cached chunks per thread (6 covers rows of up to 12288 integer columns; longer rows gather twice)
 
-  // Column ids -> shared memory, once per CTA; the pad of the last chunk repeats the first id so
-  // that it never changes the row's max/min.  16-bit ids are copied eight at a time; every warp
-  // first puts the copy of its first row in flight so that both latencies overlap.
-  const int first_row = blockIdx.x + gridDim.x * warp;
-  const bool prefetched = vec_load && warp < warps_per_cta && first_row < rows;
-  if (prefetched) {
-    const unsigned sbase = (unsigned)__cvta_generic_to_shared(s_row);
-    const uint4 *g = reinterpret_cast<const uint4 *>(src + (size_t)first_row * cols);
-    for (int i = lane; i < (cols >> 3); i += 32)
+template <typename T, int BITS, bool WIDE, typename IdxT, int NC>
+__global__ void __launch_bounds__(kQuantThreads)
+asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int_idx,
+                         const IdxT *__restrict__ fp_idx, int rows, int cols, int num_int, int num_fp,
+                         uint8_t *__restrict__ dst, T *__restrict__ meta, T *__restrict__ fp_x,
+                         int vec_load, int vec_store, int vec_ids, int nbuf) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float s_red[2][kQuantThreads / 32];
+  const int cols_pad = (cols + 7) & ~7;
+  T *s_buf = reinterpret_cast<T *>(smem_raw);          // two row buffers: the next row loads while this one is used
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int num_chunks = (num_int + 7) >> 3;
+  constexpr bool kPacked = BITS == 4 && !WIDE;
+
+  auto prefetch_row = [&](int r, int buf) {
+    const unsigned sbase = (unsigned)__cvta_generic_to_shared(s_buf + (size_t)buf * cols_pad);
+    const uint4 *g = reinterpret_cast<const uint4 *>(src + (size_t)r * cols);
+    for (int i = tid; i < (cols >> 3); i += kQuantThreads)
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sbase + i * 16), "l"(g + i));
     asm volatile("cp.async.commit_group;\n" ::: "memory");
-  }
-  if (sizeof(IdxT) == 2 && (num_int & 7) == 0 && (reinterpret_cast<uintptr_t>(int_idx) & 15) == 0) {
-    const uint4 *g = reinterpret_cast<const uint4 *>(int_idx);
-    uint4 *d = reinterpret_cast<uint4 *>(s_int);
-    for (int i = tid; i < (num_int >> 3); i += blockDim.x) d[i] = __ldg(g + i);
-  } else {
-#pragma unroll 4
-    for (int i = tid; i < int_pad; i += blockDim.x)
-      s_int[i] = static_cast<uint16_t>(i < num_int ? int_idx[i] : int_idx[0]);
-  }
-  for (int i = tid; i < num_fp; i += blockDim.x) s_fp[i] = static_cast<uint16_t>(fp_idx[i]);
-  __syncthreads();
-  if (warp >= warps_per_cta) return;
-
-  const size_t dst_pitch = (BITS == 4 && !WIDE) ? (size_t)(num_int >> 1) : (size_t)num_int;
-  // rows are dealt round-robin over the CTAs first, then over the warps of a CTA, so that a
-  // short matrix still spreads over all SMs
-  const int row_stride = gridDim.x * warps_per_cta;
-
-  for (int r = blockIdx.x + gridDim.x * warp; r < rows; r += row_stride) {
-    const T *row = src + (size_t)r * cols;
-    __syncwarp();   // previous row fully consumed by every lane
-    if (prefetched && r == first_row) {
-      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    } else if (vec_load) {
-      // global -> shared without a register round trip
-      const unsigned sbase = (unsigned)__cvta_generic_to_shared(s_row);
-      for (int i = lane; i < (cols >> 3); i += 32)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sbase + i * 16),
-                     "l"(reinterpret_cast<const uint4 *>(row) + i));
-      asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+  };
+  if (vec_load && nbuf == 2 && (int)blockIdx.x < rows) prefetch_row(blockIdx.x, 0);
+  // ids of chunk c as four words of two 16-bit ids; the pad of the last chunk repeats the first id
+  auto load_ids = [&](int c, uint32_t (&w)[4]) {
+    if (vec_ids) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4 *>(int_idx) + c);
+      w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
     } else {
-      for (int i = lane; i < cols; i += 32) s_row[i] = row[i];
-    }
-    __syncwarp();
-
-    uint8_t *drow = dst + (size_t)r * dst_pitch;
-    if (CACHE != 0) {
-      // ---------- fp16 fast path: packed arithmetic; CACHE > 0 also keeps the gathered pairs ----------
-      const unsigned short *row16 = reinterpret_cast<const unsigned short *>(s_row);
-      constexpr int NC = CACHE > 0 ? CACHE : 1;
-      uint32_t cache[NC][4];
-      __half2 mx2 = __float2half2_rn(-INFINITY), mn2 = __float2half2_rn(INFINITY);
-      auto gather_chunk = [&](int c, uint32_t (&pr)[4]) {
-        const uint4 idv = *reinterpret_cast<const uint4 *>(s_int + (c << 3));
-        const uint32_t w[4] = {idv.x, idv.y, idv.z, idv.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) pr[j] = pack_halves(row16[w[j] & 0xffffu], row16[w[j] >> 16]);
-      };
-      auto minmax_chunk = [&](const uint32_t (&pr)[4]) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          mx2 = __hmax2(mx2, *reinterpret_cast<const __half2 *>(&pr[j]));
-          mn2 = __hmin2(mn2, *reinterpret_cast<const __half2 *>(&pr[j]));
-        }
-      };
-      if (CACHE > 0) {
-#pragma unroll
-        for (int it = 0; it < NC; ++it) {
-          const int c = lane + 32 * it;
-          if (c < num_chunks) {
-            gather_chunk(c, cache[it]);
-            minmax_chunk(cache[it]);
-          }
-        }
-      } else {
-#pragma unroll 2
-        for (int c = lane; c < num_chunks; c += 32) {
-          uint32_t pr[4];
-          gather_chunk(c, pr);
-          minmax_chunk(pr);
-        }
-      }
-      float mx = warp_max(fmaxf(__low2float(mx2), __high2float(mx2)));
-      float mn = warp_min(fminf(__low2float(mn2), __high2float(mn2)));
-      const __half scale = __float2half(fmaxf((mx - mn) / (float)((1 << BITS) - 1), 1e-6f));
-      const __half zero = __float2half(mn);
-      if (lane == 0) {
-        reinterpret_cast<__half *>(meta)[2 * (size_t)r] = scale;
-        reinterpret_cast<__half *>(meta)[2 * (size_t)r + 1] = zero;
-      }
-      float rcp_scale;
-      asm("{rcp.approx.ftz.f32 %0, %1;\n}" : "=f"(rcp_scale) : "f"(__half2float(scale)));
-      const __half2 zero2 = __half2half2(zero);
-      auto emit_chunk = [&](int c, const uint32_t (&pr)[4]) {
-        uint32_t codes[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) codes[j] = codes_of_pair<BITS>(pr[j], zero2, rcp_scale);
-        uint32_t w0, w1;
-        emit_codes<BITS, (BITS == 4 && !WIDE)>(codes, w0, w1);
-        if (BITS == 4 && !WIDE) {
-          if (vec_store) {
-            *reinterpret_cast<uint32_t *>(drow + (size_t)c * 4) = w0;
-          } else {
-            const int nbytes = min(4, (num_int >> 1) - c * 4);
-            for (int j = 0; j < nbytes; ++j) drow[c * 4 + j] = (uint8_t)(w0 >> (8 * j));
-          }
-        } else {
-          if (vec_store) {
-            *reinterpret_cast<uint2 *>(drow + (size_t)c * 8) = make_uint2(w0, w1);
-          } else {
-            const int nbytes = min(8, num_int - c * 8);
-            for (int j = 0; j < nbytes; ++j)
-              drow[c * 8 + j] = (uint8_t)((j < 4 ? w0 >> (8 * j) : w1 >> (8 * (j - 4))) & 0xFF);
-          }
-        }
-      };
-      if (CACHE > 0) {
-#pragma unroll
-        for (int it = 0; it < NC; ++it) {
-          const int c = lane + 32 * it;
-          if (c < num_chunks) emit_chunk(c, cache[it]);
-        }
-      } else {
-#pragma unroll 2
-        for (int c = lane; c < num_chunks; c += 32) {
-          uint32_t pr[4];
-          gather_chunk(c, pr);
-          emit_chunk(c, pr);
-        }
-      }
-    } else {
-    // ---- pass 1: max / min over the gathered integer columns
-    float mx = -INFINITY, mn = INFINITY;
-#pragma unroll 2
-    for (int c = lane; c < num_chunks; c += 32) {
-      const uint4 idv = *reinterpret_cast<const uint4 *>(s_int + (c << 3));
-      const uint32_t w[4] = {idv.x, idv.y, idv.z, idv.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float a = Traits<T>::to_float(s_row[w[j] & 0xffffu]);
-        const float b = Traits<T>::to_float(s_row[w[j] >> 16]);
+        const int i0 = c * 8 + 2 * j, i1 = i0 + 1;
+        const uint32_t a = (uint32_t)int_idx[i0 < num_int ? i0 : 0], b = (uint32_t)int_idx[i1 < num_int ? i1 : 0];
+        w[j] = (a & 0xffffu) | (b << 16);
+      }
+    }
+  };
+  uint32_t ids[NC][4];
+#pragma unroll
+  for (int it = 0; it < NC; ++it) {
+    const int c = tid + kQuantThreads * it;
+    if (c < num_chunks) load_ids(c, ids[it]);
+  }
+
+  int buf = 0;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x, buf ^= (nbuf - 1)) {
+  T *s_row = s_buf + (size_t)buf * cols_pad;
+  const unsigned short *row16 = reinterpret_cast<const unsigned short *>(s_row);
+  if (vec_load && nbuf == 2) {
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();            // this row has landed for every thread; the other buffer is no longer read
+    if (r + (int)gridDim.x < rows) prefetch_row(r + gridDim.x, buf ^ 1);
+  } else if (vec_load) {        // very long rows: one buffer, no overlap
+    __syncthreads();
+    prefetch_row(r, 0);
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();
+  } else {
+    __syncthreads();
+    const T *row = src + (size_t)r * cols;
+    for (int i = tid; i < cols; i += kQuantThreads) s_row[i] = row[i];
+    __syncthreads();
+  }
+
+  // ---- pass 1: gather (kept in registers) and max / min
+  uint32_t pr[NC][4];
+  float mx = -INFINITY, mn = INFINITY;
+  auto gather = [&](const uint32_t (&w)[4], uint32_t (&p)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) p[j] = pack_halves(row16[w[j] & 0xffffu], row16[w[j] >> 16]);
+  };
+  auto minmax = [&](const uint32_t (&p)[4]) {
+    if (Traits<T>::kIsHalf) {
+      __half2 mx2 = __float2half2_rn(-INFINITY), mn2 = __float2half2_rn(INFINITY);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        mx2 = __hmax2(mx2, *reinterpret_cast<const __half2 *>(&p[j]));
+        mn2 = __hmin2(mn2, *reinterpret_cast<const __half2 *>(&p[j]));
+      }
+      mx = fmaxf(mx, fmaxf(__low2float(mx2), __high2float(mx2)));
+      mn = fminf(mn, fminf(__low2float(mn2), __high2float(mn2)));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const T *e = reinterpret_cast<const T *>(&p[j]);
+        const float a = Traits<T>::to_float(e[0]), b = Traits<T>::to_float(e[1]);
         mx = fmaxf(mx, fmaxf(a, b));
         mn = fminf(mn, fminf(a, b));
       }
     }
-    mx = warp_max(mx);
-    mn = warp_min(mn);
-    const T scale = Traits<T>::from_float(fmaxf((mx - mn) / (float)((1 << BITS) - 1), 1e-6f));
-    const T zero = Traits<T>::from_float(mn);           // exact: mn is a value of type T
-    if (lane == 0) {
-      meta[2 * (size_t)r] = scale;
-      meta[2 * (size_t)r + 1] = zero;
+  };
+#pragma unroll
+  for (int it = 0; it < NC; ++it) {
+    const int c = tid + kQuantThreads * it;
+    if (c < num_chunks) {
+      gather(ids[it], pr[it]);
+      minmax(pr[it]);
     }
+  }
+  for (int c = tid + kQuantThreads * NC; c < num_chunks; c += kQuantThreads) {   // very long rows
+    uint32_t w[4], p[4];
+    load_ids(c, w);
+    gather(w, p);
+    minmax(p);
+  }
+  mx = warp_max(mx);
+  mn = warp_min(mn);
+  if (lane == 0) {
+    s_red[0][warp] = mx;
+    s_red[1][warp] = mn;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < kQuantThreads / 32; ++w) {
+    mx = fmaxf(mx, s_red[0][w]);
+    mn = fminf(mn, s_red[1][w]);
+  }
+  const T scale = Traits<T>::from_float(fmaxf((mx - mn) / (float)((1 << BITS) - 1), 1e-6f));
+  const T zero = Traits<T>::from_float(mn);           // exact: mn is a value of type T
+  if (tid == 0) {
+    meta[2 * (size_t)r] = scale;
+    meta[2 * (size_t)r + 1] = zero;
+  }
 
-    // ---- pass 2: quantize + pack
-#pragma unroll 2
-    for (int c = lane; c < num_chunks; c += 32) {
-      const uint4 idv = *reinterpret_cast<const uint4 *>(s_int + (c << 3));
-      const uint32_t w[4] = {idv.x, idv.y, idv.z, idv.w};
+  // ---- pass 2: quantize + pack
+  uint8_t *drow = dst + (size_t)r * (kPacked ? (size_t)(num_int >> 1) : (size_t)num_int);
+  float rcp_scale;
+  asm("{rcp.approx.ftz.f32 %0, %1;\n}" : "=f"(rcp_scale) : "f"(Traits<T>::to_float(scale)));
+  auto emit = [&](int c, const uint32_t (&p)[4]) {
+    uint32_t w0, w1;
+    if (Traits<T>::kIsHalf) {
+      const __half2 zero2 = __half2half2(*reinterpret_cast<const __half *>(&zero));
+      uint32_t codes[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) codes[j] = codes_of_pair<BITS>(p[j], zero2, rcp_scale);
+      emit_codes<BITS, kPacked>(codes, w0, w1);
+    } else {
       int v[8];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        v[2 * j] = quantize_code<T, BITS>(s_row[w[j] & 0xffffu], zero, scale);
-        v[2 * j + 1] = quantize_code<T, BITS>(s_row[w[j] >> 16], zero, scale);
+        const T *e = reinterpret_cast<const T *>(&p[j]);
+        v[2 * j] = quantize_code<T, BITS>(e[0], zero, scale);
+        v[2 * j + 1] = quantize_code<T, BITS>(e[1], zero, scale);
       }
-      if (BITS == 4 && !WIDE) {
-        uint32_t p = 0;
+      if (kPacked) {
+        w0 = 0;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) p |= (uint32_t)(v[j] & 0xF) << (4 * j);
-        if (vec_store) {
-          *reinterpret_cast<uint32_t *>(drow + (size_t)c * 4) = p;
-        } else {
-          const int nbytes = min(4, (num_int >> 1) - c * 4);
-          for (int j = 0; j < nbytes; ++j) drow[c * 4 + j] = (uint8_t)(p >> (8 * j));
-        }
+        for (int j = 0; j < 8; ++j) w0 |= (uint32_t)(v[j] & 0xF) << (4 * j);
+        w1 = 0;
       } else {
-        uint2 p;
-        p.x = (uint32_t)(v[0] & 0xFF) | ((uint32_t)(v[1] & 0xFF) << 8) |
-              ((uint32_t)(v[2] & 0xFF) << 16) | ((uint32_t)(v[3] & 0xFF) << 24);
-        p.y = (uint32_t)(v[4] & 0xFF) | ((uint32_t)(v[5] & 0xFF) << 8) |
-              ((uint32_t)(v[6] & 0xFF) << 16) | ((uint32_t)(v[7] & 0xFF) << 24);
-        if (vec_store) {
-          *reinterpret_cast<uint2 *>(drow + (size_t)c * 8) = p;
-        } else {
-          const int nbytes = min(8, num_int - c * 8);
-          for (int j = 0; j < nbytes; ++j)
-            drow[c * 8 + j] = (uint8_t)((j < 4 ? p.x >> (8 * j) : p.y >> (8 * (j - 4))) & 0xFF);
-        }
+        w0 = (uint32_t)(v[0] & 0xFF) | ((uint32_t)(v[1] & 0xFF) << 8) | ((uint32_t)(v[2] & 0xFF) << 16) |
+             ((uint32_t)(v[3] & 0xFF) << 24);
+        w1 = (uint32_t)(v[4] & 0xFF) | ((uint32_t)(v[5] & 0xFF) << 8) | ((uint32_t)(v[6] & 0xFF) << 16) |
+             ((uint32_t)(v[7] & 0xFF) << 24);
       }
     }
-
+    if (kPacked) {
+      if (vec_store) {
+        *reinterpret_cast<uint32_t *>(drow + (size_t)c * 4) = w0;
+      } else {
+        const int nbytes = min(4, (num_int >> 1) - c * 4);
+        for (int j = 0; j < nbytes; ++j) drow[c * 4 + j] = (uint8_t)(w0 >> (8 * j));
+      }
+    } else {
+      if (vec_store) {
+        *reinterpret_cast<uint2 *>(drow + (size_t)c * 8) = make_uint2(w0, w1);
+      } else {
+        const int nbytes = min(8, num_int - c * 8);
+        for (int j = 0; j < nbytes; ++j)
+          drow[c * 8 + j] = (uint8_t)((j < 4 ? w0 >> (8 * j) : w1 >> (8 * (j - 4))) & 0xFF);
+      }
     }
+  };
+#pragma unroll
+  for (int it = 0; it < NC; ++it) {
+    const int c = tid + kQuantThreads * it;
+    if (c < num_chunks) emit(c, pr[it]);
+  }
+  for (int c = tid + kQuantThreads * NC; c < num_chunks; c += kQuantThreads) {
+    uint32_t w[4], p[4];
+    load_ids(c, w);
+    gather(w, p);
+    emit(c, p);
+  }
 
-    // ---- outlier columns, verbatim
-    T *frow = fp_x + (size_t)r * num_fp;
-    for (int j = lane; j < num_fp; j += 32) frow[j] = s_row[s_fp[j]];
+  // ---- outlier columns, verbatim
+  T *frow = fp_x + (size_t)r * num_fp;
+  for (int j = tid; j < num_fp; j += kQuantThreads) frow[j] = s_row[(int)fp_idx[j]];
   }
 }
 
-template <typename T, int BITS, bool WIDE, typename IdxT, int CACHE>
-int launch_asym_cached(const void *src, int rows, int cols, const void *int_idx, int num_int,
-                  const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x,
-                  cudaStream_t st) {
-  const int int_pad = ((num_int + 7) >> 3) << 3, fp_pad = (num_fp + 7) & ~7,
-            cols_pad = (cols + 7) & ~7;
-  const size_t idx_bytes = (size_t)(int_pad + fp_pad) * 2, row_bytes = (size_t)cols_pad * sizeof(T);
-  // as many warps (rows in flight) per CTA as shared memory allows, at most 8
-  const size_t budget = 200 * 1024;
-  int warps = (int)((budget - idx_bytes) / row_bytes);
-  if (warps < 1) return QUIK_ERR_UNSUPPORTED;
-  if (warps > kQuantThreads / 32) warps = kQuantThreads / 32;
-  // small rows: keep the CTA at 8 warps but do not let one CTA hog an SM's shared memory
-  const size_t smem = idx_bytes + (size_t)warps * row_bytes;
-  auto kern = asym_quantize_kernel<T, BITS, WIDE, IdxT, CACHE>;
+template <typename T, int BITS, bool WIDE, typename IdxT, int NC>
+int launch_asym_rows_nc(const void *src, int rows, int cols, const void *int_idx, int num_int,
+                     const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x, cudaStream_t st) {
+  const size_t row_bytes = (size_t)((cols + 7) & ~7) * sizeof(T);
+  const int nbuf = 2 * row_bytes <= 200 * 1024 ? 2 : 1;
+  const size_t smem = nbuf * row_bytes;
+  if (smem > 200 * 1024) return QUIK_ERR_UNSUPPORTED;
+  auto kern = asym_quantize_row_kernel<T, BITS, WIDE, IdxT, NC>;
   // attribute and occupancy are looked up once per (instantiation, shared-memory size)
   static size_t cached_smem = 0;
   static int cached_per_sm = 0;
@@ -324,31 +293,27 @@ int launch_asym_cached(const void *src, int rows, int cols, const void *int_idx,
     cached_smem = smem;
     cached_per_sm = occ;
   }
-  const int per_sm = cached_per_sm;
-  const int grid = max(1, min(rows, num_sms() * per_sm));
+  const int grid = min(rows, num_sms() * cached_per_sm);
   const int vec_load = (cols % 8 == 0) && aligned16(src);
   const bool packed = (BITS == 4 && !WIDE);
-  const int vec_store = (num_int % 8 == 0) &&
-                        ((reinterpret_cast<uintptr_t>(dst) & (packed ? 3u : 7u)) == 0);
-  kern<<<grid, kQuantThreads, smem, st>>>(
-      static_cast<const T *>(src), static_cast<const IdxT *>(int_idx),
-      static_cast<const IdxT *>(fp_idx), rows, cols, num_int, num_fp, static_cast<uint8_t *>(dst),
-      static_cast<T *>(meta), static_cast<T *>(fp_x), vec_load, vec_store, warps);
-  return check_launch("asym_quantize_kernel");
+  const int vec_store = (num_int % 8 == 0) && ((reinterpret_cast<uintptr_t>(dst) & (packed ? 3u : 7u)) == 0);
+  const int vec_ids = sizeof(IdxT) == 2 && (num_int % 8 == 0) && aligned16(int_idx);
+  kern<<<grid, kQuantThreads, smem, st>>>(static_cast<const T *>(src), static_cast<const IdxT *>(int_idx),
+                                          static_cast<const IdxT *>(fp_idx), rows, cols, num_int, num_fp,
+                                          static_cast<uint8_t *>(dst), static_cast<T *>(meta),
+                                          static_cast<T *>(fp_x), vec_load, vec_store, vec_ids, nbuf);
+  return check_launch("asym_quantize_row_kernel");
 }
 
-// fp16 rows of up to 16 chunks per lane (4096 integer columns) take the register-cached packed path
 template <typename T, int BITS, bool WIDE, typename IdxT>
-int launch_asym_t(const void *src, int rows, int cols, const void *int_idx, int num_int,
-                  const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x,
-                  cudaStream_t st) {
-  constexpr bool is_half = sizeof(T) == 2 && Traits<T>::kIsHalf;
-  if (is_half && num_int <= 8 * 32 * 16)
-    return launch_asym_cached<T, BITS, WIDE, IdxT, is_half ? 16 : 0>(src, rows, cols, int_idx, num_int, fp_idx, num_fp,
-                                                                      dst, meta, fp_x, st);
-  // longer fp16 rows: same packed arithmetic, values gathered in both passes; bf16: scalar intrinsics
-  return launch_asym_cached<T, BITS, WIDE, IdxT, is_half ? -1 : 0>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
-                                                                    meta, fp_x, st);
+int launch_asym_rows(const void *src, int rows, int cols, const void *int_idx, int num_int,
+                     const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x, cudaStream_t st) {
+  const int per_thread = (((num_int + 7) >> 3) + kQuantThreads - 1) / kQuantThreads;
+  if (per_thread <= 2)
+    return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 2>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+  if (per_thread <= 4)
+    return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 4>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+  return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 6>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
 }
 
 template <typename T, typename IdxT>
@@ -356,12 +321,12 @@ int dispatch_bits(int bits, int wide, const void *src, int rows, int cols, const
                   int num_int, const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x,
                   cudaStream_t st) {
   if (bits == 8)
-    return launch_asym_t<T, 8, true, IdxT>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
+    return launch_asym_rows<T, 8, true, IdxT>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
                                            meta, fp_x, st);
   if (wide)
-    return launch_asym_t<T, 4, true, IdxT>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
+    return launch_asym_rows<T, 4, true, IdxT>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
                                            meta, fp_x, st);
-  return launch_asym_t<T, 4, false, IdxT>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
+  return launch_asym_rows<T, 4, false, IdxT>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
                                           meta, fp_x, st);
 }
 

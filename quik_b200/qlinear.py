@@ -133,15 +133,20 @@ class MixedQLinear(torch.nn.Module):
             return self._forward_unfused(x, shared_input)
 
         M = x.shape[0]
-        wide = M > _lib.SMALL_M_MAX          # tensor-core engine above, weight streaming below
+        # Above SMALL_M_MAX tokens: tensor-core GEMM on codes widened to one per byte (both operands).  Below:
+        # weight streaming, the weights stay packed; the tcgen05 engine takes the token codes one per byte, the
+        # mma.sync engine (the default for 4-bit layers: faster on the layer sizes measured) packed like the weights.
+        stream = M <= _lib.SMALL_M_MAX and _lib.small_m_mode != _lib.SMALL_M_OFF
+        wide = not (stream and _lib.small_m_mode != _lib.SMALL_M_TCGEN05)
         if shared_input.qint_x is None:
             i16, f16 = self._idx16()
             shared_input.qint_x, shared_input.meta, shared_input.fp_x = asymmetric.quantize_u16(
                 x, i16, f16, self.bits, wide)
             shared_input.wide = wide
         q = shared_input.qint_x
-        packed = self.bits == 4 and not shared_input.wide
-        w = self.int_weight if (packed or self.bits == 8) else self._weight_codes_int8()
+        q_packed = self.bits == 4 and not shared_input.wide
+        w_packed = self.bits == 4 and (stream or q_packed)
+        w = self.int_weight if (w_packed or self.bits == 8) else self._weight_codes_int8()
         N = self.out_features
         hook = MixedQLinear.launch_hook
         with torch.cuda.device(x.device):
@@ -155,7 +160,7 @@ class MixedQLinear(torch.nn.Module):
             if hook is not None:
                 hook(self, True)
             check(load().quik_mixed_linear_ld(
-                ptr(q), int(packed), ptr(w), int(packed), ptr(shared_input.meta), ptr(self.weights_scales),
+                ptr(q), int(q_packed), ptr(w), int(w_packed), ptr(shared_input.meta), ptr(self.weights_scales),
                 ptr(self.reduced_w), ptr(shared_input.fp_x) if F > 0 else None,
                 ptr(self.fp_weight) if F > 0 else None, ptr(self.bias) if self.bias is not None else None,
                 ptr(out), out.stride(0), dtype_code(x.dtype), M, N, self.int_features_num, F, self.bits, stream_of(x)),

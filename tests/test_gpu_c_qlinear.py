@@ -49,6 +49,41 @@ def test_fused_forward_matches_oracle(dtype, M, K, N, F, bits):
     assert_device_clean()
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,N,F,bits", [
+    (16, 256, 128, 0, 4), (16, 1280, 128, 256, 8), (1, 4352, 512, 256, 4), (16, 4352, 264, 256, 4), (7, 11264, 256, 256, 8),
+    (16, 4352, 4096, 256, 4),      # K split over a cluster of 4 CTAs
+    (13, 11264, 4096, 256, 8),     # ... of 8
+    (16, 4352, 22016, 256, 4),     # one CTA per slab, more slabs than fit at once
+    (5, 4232, 300, 72, 4),         # ragged N, K and F
+])
+def test_small_m_engines_agree(dtype, M, K, N, F, bits):
+    """Few tokens: both weight-streaming engines (tcgen05 with on-chip widening, mma.sync) and the tensor-core
+    GEMM on widened weights give the oracle's result; the integer part is exact in all three."""
+    case = make_layer("t", M, K, N, bits, F=F, seed=M + N, device=dev(), dtype=dtype, clip=False)
+    outs = {}
+    try:
+        for mode in (_lib.SMALL_M_TCGEN05, _lib.SMALL_M_MMA_SYNC, _lib.SMALL_M_OFF, _lib.SMALL_M_AUTO):
+            _lib.set_small_m(mode)
+            outs[mode] = case.module(case.x.unsqueeze(0))[0].clone()
+            again = case.module(case.x.unsqueeze(0))[0]
+            assert torch.equal(outs[mode], again)                # deterministic (split-K included)
+    finally:
+        _lib.set_small_m(_lib.SMALL_M_AUTO)
+    assert_device_clean()
+    ref = _oracle_out(case, round_y=False)
+    tol = TOL_RMS if dtype == torch.float16 else 4e-2
+    for mode, out in outs.items():
+        assert rel_rms_err(out.cpu(), ref) < tol, mode
+    # the engines differ only in the summation order of the outlier product: at most one unit in the last place of
+    # the largest outputs (2^-10 of 4 x RMS in fp16)
+    agree = 5e-3 if dtype == torch.float16 else 4e-2
+    assert rel_rms_err(outs[_lib.SMALL_M_TCGEN05], outs[_lib.SMALL_M_MMA_SYNC]) < agree
+    assert rel_rms_err(outs[_lib.SMALL_M_TCGEN05], outs[_lib.SMALL_M_OFF]) < agree
+    if F == 0:
+        assert torch.equal(outs[_lib.SMALL_M_TCGEN05], outs[_lib.SMALL_M_MMA_SYNC])
+
+
 @pytest.mark.parametrize("pair", [1, 2])
 @pytest.mark.parametrize("M,K,N,F,bits", [(300, 4096, 520, 256, 4), (2048, 4096, 2048, 256, 4), (640, 11008, 512, 256, 8),
                                           (128, 1024, 256, 64, 4), (513, 2048, 1000, 0, 4)])
