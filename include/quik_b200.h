@@ -52,6 +52,11 @@ extern "C" {
 #define QUIK_CFG_SMALL_M       3
 /* CTA pairs (cta_group::2, 256-row tiles) in the tcgen05 engine: 0 = when M > 128, 1 = never, 2 = always. */
 #define QUIK_CFG_CTA_PAIR      4
+/* Programmatic dependent launch of the layer's kernels (quantizer, GEMM, weight streaming): 1 (default) a
+ * kernel may start, set up and ask L2 to prefetch its weights while its predecessor in the stream still runs;
+ * it waits for the predecessor's completion before its first global load or store, so results are those of
+ * plain stream order; 0 launches in plain stream order. */
+#define QUIK_CFG_PDL           5
 
 const char *quik_version(void);
 const char *quik_strerror(int status);

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libquik_b200.so")
 
 QUIK_OK = 0
 F16, BF16 = 0, 1
-CFG_GEMM_ENGINE, CFG_TILE_N, CFG_SMALL_M, CFG_CTA_PAIR = 1, 2, 3, 4
+CFG_GEMM_ENGINE, CFG_TILE_N, CFG_SMALL_M, CFG_CTA_PAIR, CFG_PDL = 1, 2, 3, 4, 5
 ENGINE_AUTO, ENGINE_TCGEN05, ENGINE_MMA_SYNC = 0, 1, 2
 SMALL_M_MAX = 16
 
@@ -134,6 +134,11 @@ def set_small_m(mode) -> None:
     mode = int(mode)
     check(load().quik_config_set(CFG_SMALL_M, mode), "quik_config_set")
     small_m_mode = mode
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch of the layer's kernels (default on); off = plain stream order."""
+    check(load().quik_config_set(CFG_PDL, int(bool(on))), "quik_config_set")
 
 
 def device_status(clear: bool = True) -> int:

@@ -12,11 +12,14 @@ namespace {
 thread_local char g_err[256] = "";
 int g_engine = QUIK_ENGINE_AUTO;
 int g_small_m = 1;
+int g_pdl = 1;
 }  // namespace
 
 void set_cuda_error(cudaError_t e, const char *where) {
   snprintf(g_err, sizeof(g_err), "%s: %s", where, cudaGetErrorString(e));
 }
+
+bool pdl_enabled() { return g_pdl != 0; }
 
 int num_sms() {
   static int cached[64];
@@ -81,6 +84,10 @@ int quik_config_set(int key, int value) {
     g_small_m = value;
     return QUIK_OK;
   }
+  if (key == QUIK_CFG_PDL) {
+    g_pdl = value ? 1 : 0;
+    return QUIK_OK;
+  }
   if (key == QUIK_CFG_CTA_PAIR) {
     if (value < 0 || value > 2) return QUIK_ERR_UNSUPPORTED;
     set_cta_pair(value);
@@ -91,6 +98,7 @@ int quik_config_set(int key, int value) {
 
 int quik_config_get(int key) {
   if (key == QUIK_CFG_SMALL_M) return g_small_m;
+  if (key == QUIK_CFG_PDL) return g_pdl;
   if (key == QUIK_CFG_CTA_PAIR) return get_cta_pair();
   if (key == QUIK_CFG_GEMM_ENGINE) return g_engine;
   if (key == QUIK_CFG_TILE_N) return get_tile_n();

@@ -33,6 +33,48 @@ inline int check_launch(const char *what) {
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ---- launches with programmatic dependent launch ----------------------------------------------
+// The layer's kernels (quantizer, GEMM, weight-streaming engines) are launched so that a kernel may start
+// while its predecessor in the stream is still running: it sets up (barriers, TMEM, descriptors), asks L2 to
+// prefetch its weights (a prefetch returns nothing to the SM and L2 is coherent, so this is safe whoever
+// writes that memory) and only then waits for the predecessor to complete (pdl_wait) before its first global
+// load or store.  Every kernel launched through LaunchCfg must call pdl_wait() before that point.
+// QUIK_CFG_PDL = 0 restores plain stream order.
+bool pdl_enabled();                                      // abi.cu
+
+struct LaunchCfg {
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attrs[2];
+  LaunchCfg(dim3 grid, dim3 block, size_t smem, cudaStream_t st, int cluster_x = 1) : cfg{} {
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    unsigned n = 0;
+    if (cluster_x > 1) {
+      attrs[n].id = cudaLaunchAttributeClusterDimension;
+      attrs[n].val.clusterDim.x = (unsigned)cluster_x;
+      attrs[n].val.clusterDim.y = 1;
+      attrs[n].val.clusterDim.z = 1;
+      ++n;
+    }
+    if (pdl_enabled()) {
+      attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attrs[n].val.programmaticStreamSerializationAllowed = 1;
+      ++n;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = n;
+  }
+};
+
+#ifdef __CUDACC__
+// dependents of this grid may be launched (they still wait for its completion in pdl_wait)
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// all grids this one depends on have completed and their writes are visible
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+
 // ---- device status word (bounded waits report here); lives in gemm_tcgen05.cu ---------------
 int device_status_read(int clear);   // synchronises the device
 void set_tile_n(int n);               // 0 = by shape, 128 or 256

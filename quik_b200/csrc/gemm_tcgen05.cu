@@ -167,6 +167,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(full_bar + s), 1);
@@ -197,6 +198,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   if (CTAS == 2) cluster_sync_all();          // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                                 // set-up done; everything below reads or writes global memory
 
   const int rank = CTAS == 2 ? (int)cluster_ctarank() : 0;
   const int unit = (int)blockIdx.x / CTAS, num_units = (int)gridDim.x / CTAS;    // a unit = CTA or CTA pair
@@ -626,23 +628,8 @@ int launch_t(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tf
   }
   if (resident_units <= 0) return QUIK_ERR_UNSUPPORTED;
   const int units = p.num_tiles < resident_units ? p.num_tiles : resident_units;
-  if (CTAS == 1) {
-    kern<<<units, NUM_THREADS, smem, st>>>(ta, tb, tfa, tfb, p);
-  } else {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * units);
-    cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    QUIK_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, tfa, tfb, p));
-  }
+  LaunchCfg lc(dim3(CTAS * units), dim3(NUM_THREADS), smem, st, CTAS);
+  QUIK_CUDA_TRY(cudaLaunchKernelEx(&lc.cfg, kern, ta, tb, tfa, tfb, p));
   return check_launch("gemm_tcgen05_kernel");
 }
 

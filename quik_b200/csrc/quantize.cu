@@ -96,6 +96,7 @@ asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int num_chunks = (num_int + 7) >> 3;
   constexpr bool kPacked = BITS == 4 && !WIDE;
+  pdl_launch_dependents();
 
   auto prefetch_row = [&](int r, int buf) {
     const unsigned sbase = (unsigned)__cvta_generic_to_shared(s_buf + (size_t)buf * cols_pad);
@@ -104,7 +105,6 @@ asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sbase + i * 16), "l"(g + i));
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
-  if (vec_load && nbuf == 2 && (int)blockIdx.x < rows) prefetch_row(blockIdx.x, 0);
   // ids of chunk c as four words of two 16-bit ids; the pad of the last chunk repeats the first id
   auto load_ids = [&](int c, uint32_t (&w)[4]) {
     if (vec_ids) {
@@ -119,6 +119,8 @@ asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int
       }
     }
   };
+  pdl_wait();       // the producer of `src` has completed; nothing global was touched before this point
+  if (vec_load && nbuf == 2 && (int)blockIdx.x < rows) prefetch_row(blockIdx.x, 0);
   uint32_t ids[NC][4];
 #pragma unroll
   for (int it = 0; it < NC; ++it) {
@@ -298,10 +300,11 @@ int launch_asym_rows_nc(const void *src, int rows, int cols, const void *int_idx
   const bool packed = (BITS == 4 && !WIDE);
   const int vec_store = (num_int % 8 == 0) && ((reinterpret_cast<uintptr_t>(dst) & (packed ? 3u : 7u)) == 0);
   const int vec_ids = sizeof(IdxT) == 2 && (num_int % 8 == 0) && aligned16(int_idx);
-  kern<<<grid, kQuantThreads, smem, st>>>(static_cast<const T *>(src), static_cast<const IdxT *>(int_idx),
-                                          static_cast<const IdxT *>(fp_idx), rows, cols, num_int, num_fp,
-                                          static_cast<uint8_t *>(dst), static_cast<T *>(meta),
-                                          static_cast<T *>(fp_x), vec_load, vec_store, vec_ids, nbuf);
+  LaunchCfg lc(dim3(grid), dim3(kQuantThreads), smem, st);
+  QUIK_CUDA_TRY(cudaLaunchKernelEx(&lc.cfg, kern, static_cast<const T *>(src), static_cast<const IdxT *>(int_idx),
+                                   static_cast<const IdxT *>(fp_idx), rows, cols, num_int, num_fp,
+                                   static_cast<uint8_t *>(dst), static_cast<T *>(meta), static_cast<T *>(fp_x),
+                                   vec_load, vec_store, vec_ids, nbuf));
   return check_launch("asym_quantize_row_kernel");
 }
 

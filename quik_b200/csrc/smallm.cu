@@ -103,6 +103,22 @@ small_m_kernel(const uint8_t *__restrict__ q, const uint8_t *__restrict__ w, int
     w_row[nt] = w + (size_t)wr * row_bytes;
     fw_row[nt] = reinterpret_cast<const uint8_t *>(fp_w) + (size_t)wr * fp_bytes;
   }
+  // Ask L2 for this CTA's share of the weights (all of it: 8*NT rows), then wait for the kernel that produces
+  // the token codes: the weight stream from HBM overlaps that kernel and its launch.
+  pdl_launch_dependents();
+  {
+    const int lines_per_row = (row_bytes + 127) >> 7, fp_lines = (fp_bytes + 127) >> 7;
+    const int rows_here = min(8 * NT, N - n0);
+    for (int i = threadIdx.x; i < rows_here * lines_per_row; i += SM_THREADS) {
+      const int rr = i / lines_per_row, ln = i - rr * lines_per_row;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(w + (size_t)(n0 + rr) * row_bytes + (size_t)ln * 128));
+    }
+    for (int i = threadIdx.x; i < rows_here * fp_lines; i += SM_THREADS) {
+      const int rr = i / fp_lines, ln = i - rr * fp_lines;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(fp_w) + (size_t)(n0 + rr) * fp_bytes + (size_t)ln * 128));
+    }
+  }
+  pdl_wait();
   const uint8_t *q_lo = q + (size_t)g * row_bytes;
   const uint8_t *q_hi = q + (size_t)(g + 8) * row_bytes;
   const uint8_t *fx_lo = reinterpret_cast<const uint8_t *>(fp_x) + (size_t)g * fp_bytes;
@@ -226,12 +242,14 @@ int launch_small_m(const void *q, const void *w, int bits, int M, int N, int K_i
   const int sms = num_sms();
   const int nt = (N >= 64 * sms) ? 4 : (N >= 32 * sms ? 2 : 1);
   const int grid = (N + 8 * nt - 1) / (8 * nt);
+  LaunchCfg lc(dim3(grid), dim3(SM_THREADS), 0, st);
 #define QUIK_SM(T, B, NT)                                                                                 \
-  small_m_kernel<T, B, NT><<<grid, SM_THREADS, 0, st>>>(                                                  \
-      static_cast<const uint8_t *>(q), static_cast<const uint8_t *>(w), M, N, row_bytes,                 \
-      static_cast<const T *>(ep.fp_a), static_cast<const T *>(ep.fp_b), ep.F, static_cast<const T *>(ep.meta), \
-      static_cast<const T *>(ep.scale_col), static_cast<const T *>(ep.w_reduced),                         \
-      static_cast<const T *>(ep.bias), static_cast<T *>(ep.out), ep.ldo > 0 ? ep.ldo : (long long)N)
+  QUIK_CUDA_TRY(cudaLaunchKernelEx(                                                                       \
+      &lc.cfg, small_m_kernel<T, B, NT>, static_cast<const uint8_t *>(q), static_cast<const uint8_t *>(w), M, N, \
+      row_bytes, static_cast<const T *>(ep.fp_a), static_cast<const T *>(ep.fp_b), ep.F,                  \
+      static_cast<const T *>(ep.meta), static_cast<const T *>(ep.scale_col),                              \
+      static_cast<const T *>(ep.w_reduced), static_cast<const T *>(ep.bias), static_cast<T *>(ep.out),    \
+      ep.ldo > 0 ? ep.ldo : (long long)N))
 #define QUIK_SM_NT(T, B)                                                                                  \
   do {                                                                                                    \
     if (nt == 4) QUIK_SM(T, B, 4);                                                                        \

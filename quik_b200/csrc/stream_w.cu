@@ -81,6 +81,9 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
         "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
       : "memory");
 }
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -143,6 +146,7 @@ stream_w_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   const int n_int = nb - n_fp;
   const int kb_first = c0 + n_fp - p.nf;                           // first integer k-block
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < SW_STAGES; ++s) {
       mbar_init(smem_u32(full_bar + s), 1);
@@ -167,6 +171,13 @@ stream_w_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     tmem_alloc<1>(smem_u32(tmem_slot), SW_TMEM_COLS);
     tmem_relinquish<1>();
   }
+  if (warp == 0 && lane < SW_STAGES && lane < nb) {
+    // ask L2 for the weight tiles of the first blocks while the producer of the token codes still runs
+    const int i = lane;
+    if (i < n_fp) tma_prefetch_2d(&tm_fw, (c0 + i) * 64, n0);
+    else tma_prefetch_2d(&tm_w, (kb_first + i - n_fp) * 128, n0);
+  }
+  pdl_wait();      // first global access below
   if (worker) {
     const int te = threadIdx.x - 64;
     if (S > 1 && rank == 0)
@@ -433,19 +444,8 @@ int launch_t(const CUtensorMap &tw, const CUtensorMap &tx, const CUtensorMap &tf
     QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SW_SMEM));
     configured = true;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(slabs * p.splits);
-  cfg.blockDim = dim3(SW_THREADS);
-  cfg.dynamicSmemBytes = SW_SMEM;
-  cfg.stream = st;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = p.splits;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
-  QUIK_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tw, tx, tfw, tfx, p));
+  LaunchCfg lc(dim3(slabs * p.splits), dim3(SW_THREADS), SW_SMEM, st, p.splits);
+  QUIK_CUDA_TRY(cudaLaunchKernelEx(&lc.cfg, kern, tw, tx, tfw, tfx, p));
   return check_launch("stream_w_kernel");
 }
 

@@ -84,6 +84,63 @@ def test_small_m_engines_agree(dtype, M, K, N, F, bits):
         assert torch.equal(outs[_lib.SMALL_M_TCGEN05], outs[_lib.SMALL_M_MMA_SYNC])
 
 
+@pytest.mark.parametrize("M", [16, 300])
+def test_dependent_launch_matches_stream_order(M):
+    """A chain of layers (each output feeds the next quantizer) with kernels launched as programmatic dependents
+    gives bit-identical results to plain stream order, eagerly and replayed from a CUDA graph."""
+    cases = [make_layer(f"l{i}", M, 1024 + 64, 1024 + 64, 4 if i % 2 == 0 else 8, F=64, seed=i, device=dev(), clip=False)
+             for i in range(4)]
+    x0 = cases[0].x
+
+    def chain():
+        h = x0
+        for c in cases:
+            h = c.module(h.unsqueeze(0))[0]
+            h = (h / h.float().abs().max().clamp_min(1e-3)).to(x0.dtype)     # keep magnitudes stable (a torch kernel in between)
+        return h
+
+    try:
+        _lib.set_pdl(False)
+        ref = chain().clone()
+        _lib.set_pdl(True)
+        eager = chain().clone()
+        torch.cuda.synchronize()
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                out = chain()
+            for _ in range(3):
+                g.replay()
+        torch.cuda.synchronize()
+    finally:
+        _lib.set_pdl(True)
+    assert torch.equal(eager, ref)
+    assert torch.equal(out, ref)
+    assert_device_clean()
+
+
+def test_dependent_launch_back_to_back_layers():
+    """Layers launched back to back with no other kernel in between (shared quantized input: quantizer, then three
+    fused launches), where a launch can overtake its predecessor's tail; outputs equal plain stream order."""
+    shared = SharedQuantizedInput(3)
+    cases = [make_layer(f"m{i}", 16, 4096 + 256, 1024, 4, F=256, seed=0, device=dev(), shared_input=shared, clip=False)
+             for i in range(3)]
+    x = cases[0].x
+    res = {}
+    try:
+        for on in (False, True):
+            _lib.set_pdl(on)
+            for rep in range(3):
+                res[on] = [c.module(x.unsqueeze(0)).clone() for c in cases]
+        torch.cuda.synchronize()
+    finally:
+        _lib.set_pdl(True)
+    for a, b in zip(res[False], res[True]):
+        assert torch.equal(a, b)
+    assert_device_clean()
+
+
 @pytest.mark.parametrize("pair", [1, 2])
 @pytest.mark.parametrize("M,K,N,F,bits", [(300, 4096, 520, 256, 4), (2048, 4096, 2048, 256, 4), (640, 11008, 512, 256, 8),
                                           (128, 1024, 256, 64, 4), (513, 2048, 1000, 0, 4)])
