@@ -46,9 +46,10 @@ extern "C" {
 #define QUIK_ENGINE_MMA_SYNC   2
 /* Output-tile width of the tcgen05 engine: 0 = chosen by shape, 128 or 256. */
 #define QUIK_CFG_TILE_N        2
-/* int8 layers with M <= QUIK_SMALL_M_MAX tokens: 1 (default) weight streaming, engine chosen by the size of the
- * weights; 2 weight streaming on mma.sync; 3 weight streaming on tcgen05; 0 the tensor-core GEMM.
- * (4-bit layers choose by the operand layout, see quik_mixed_linear.) */
+/* Layers with M <= QUIK_SMALL_M_MAX tokens: 1 (default) weight streaming, engine chosen by the size of the
+ * weights; 2 mma.sync fed by direct loads; 3 tcgen05 fed by a TMA ring (8-bit layers, and 4-bit layers whose token
+ * codes come one per byte); 4 mma.sync fed by a TMA ring; 0 the tensor-core GEMM for 8-bit layers.
+ * (4-bit layers also choose by the operand layout, see quik_mixed_linear.) */
 #define QUIK_CFG_SMALL_M       3
 /* CTA pairs (cta_group::2, 256-row tiles) in the tcgen05 engine: 0 = when M > 128, 1 = never, 2 = always. */
 #define QUIK_CFG_CTA_PAIR      4
@@ -197,7 +198,8 @@ int quik_fused_dequantize(const void *A, const void *B, int bits,
  *   q one per byte, w one per byte   tensor-core GEMM (any M);
  *   q one per byte, w packed         weight streaming on tcgen05 (M <= QUIK_SMALL_M_MAX, K_int % 32 == 0): the
  *                                    packed weights are widened on chip on their way to the tensor cores;
- *   q packed,       w packed         weight streaming on mma.sync (M <= QUIK_SMALL_M_MAX, K_int % 32 == 0).
+ *   q packed,       w packed         weight streaming on mma.sync, direct loads or TMA ring by QUIK_CFG_SMALL_M
+ *                                    (M <= QUIK_SMALL_M_MAX, K_int % 32 == 0).
  * K_int % 16 == 0, F % 8 == 0. */
 #define QUIK_SMALL_M_MAX 16
 int quik_mixed_linear(const void *q, int q_packed, const void *w, int w_packed,

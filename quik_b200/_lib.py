@@ -122,14 +122,14 @@ def set_cta_pair(mode: int) -> None:
     check(load().quik_config_set(CFG_CTA_PAIR, mode), "quik_config_set")
 
 
-SMALL_M_OFF, SMALL_M_AUTO, SMALL_M_MMA_SYNC, SMALL_M_TCGEN05 = 0, 1, 2, 3
+SMALL_M_OFF, SMALL_M_AUTO, SMALL_M_MMA_SYNC, SMALL_M_TCGEN05, SMALL_M_TMA_MMA = 0, 1, 2, 3, 4
 small_m_mode = SMALL_M_AUTO      # mirror of QUIK_CFG_SMALL_M, read by MixedQLinear on every call
 
 
 def set_small_m(mode) -> None:
     """Engine for layers with at most SMALL_M_MAX tokens: 0 = none (tensor-core GEMM on widened weights),
-    1 / True = weight streaming, engine by layer (4-bit: mma.sync; 8-bit: by weight size), 2 = weight
-    streaming on mma.sync, 3 = weight streaming on tcgen05."""
+    1 / True = weight streaming, engine by layer size, 2 = mma.sync fed by direct loads, 3 = tcgen05 fed by a TMA
+    ring, 4 = mma.sync fed by a TMA ring."""
     global small_m_mode
     mode = int(mode)
     check(load().quik_config_set(CFG_SMALL_M, mode), "quik_config_set")

@@ -80,7 +80,7 @@ int quik_config_set(int key, int value) {
     return QUIK_OK;
   }
   if (key == QUIK_CFG_SMALL_M) {
-    if (value < 0 || value > 3) return QUIK_ERR_UNSUPPORTED;
+    if (value < 0 || value > 4) return QUIK_ERR_UNSUPPORTED;
     g_small_m = value;
     return QUIK_OK;
   }
@@ -314,15 +314,25 @@ int quik_mixed_linear_ld(const void *q, int q_packed, const void *w, int w_packe
     // packed int4 weights: weight-streaming engines (few tokens only)
     if (!w_packed) return QUIK_ERR_UNSUPPORTED;
     if (K_int % 32 != 0) return QUIK_ERR_SHAPE;
-    if (q_packed) return launch_small_m(q, w, 4, M, N, K_int, ep, st);      // mma.sync, both operands packed
+    if (q_packed) {
+      // mma.sync engines, both operands packed.  Automatic mode: layers of >= 16 MiB of packed weights go
+      // through the TMA-fed ring (it streams faster), smaller ones to the direct-load kernel (it starts faster).
+      const bool ring = g_small_m == 4 || (g_small_m == 1 && (size_t)N * (size_t)K_int / 2 >= ((size_t)16 << 20));
+      return ring ? launch_stream_w_mma(q, w, 4, M, N, K_int, ep, st) : launch_small_m(q, w, 4, M, N, K_int, ep, st);
+    }
     return launch_stream_w(q, w, 4, M, N, K_int, ep, st);                   // tcgen05, token codes one per byte
   }
-  // one code per byte: int8 layers with few tokens also stream their weights.  In automatic mode the tcgen05
-  // engine takes the large layers (it holds 0.85 of the HBM rate there, the mma.sync engine 0.58) and the
-  // mma.sync engine the small ones, where its shorter start-up counts for more.
+  // one code per byte: int8 layers with few tokens also stream their weights.  Automatic mode, by the size of the
+  // weights (measured on 7B and 70B down projections): >= 128 MiB tcgen05 (0.91 of the HBM rate), >= 32 MiB mma.sync
+  // behind the TMA ring (0.87 on the large layer, the fastest on the 45 MiB one), below that mma.sync with direct
+  // loads (shortest start-up).
   if (bits == 8 && M <= QUIK_SMALL_M_MAX && g_small_m != 0) {
-    const bool tc = g_small_m == 3 || (g_small_m == 1 && (size_t)N * (size_t)K_int >= ((size_t)64 << 20));
-    return tc ? launch_stream_w(q, w, 8, M, N, K_int, ep, st) : launch_small_m(q, w, 8, M, N, K_int, ep, st);
+    const size_t wbytes = (size_t)N * (size_t)K_int;
+    int engine = g_small_m;
+    if (engine == 1) engine = wbytes >= ((size_t)128 << 20) ? 3 : (wbytes >= ((size_t)32 << 20) ? 4 : 2);
+    if (engine == 3) return launch_stream_w(q, w, 8, M, N, K_int, ep, st);
+    if (engine == 4) return launch_stream_w_mma(q, w, 8, M, N, K_int, ep, st);
+    return launch_small_m(q, w, 8, M, N, K_int, ep, st);
   }
   return run_int8_gemm(static_cast<const int8_t *>(q), static_cast<const int8_t *>(w), M, N, K_int, ep, st);
 }

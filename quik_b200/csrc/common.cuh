@@ -155,6 +155,9 @@ int launch_gemm_mma_sync(const int8_t *A, const int8_t *B, int M, int N, int K, 
                          cudaStream_t st);
 int launch_small_m(const void *q, const void *w, int bits, int M, int N, int K_int,
                    const Epilogue &ep, cudaStream_t st);
+// TMA-fed mma.sync weight streaming (stream_w_mma.cu): q and w in the reference's storage format
+int launch_stream_w_mma(const void *q, const void *w, int bits, int M, int N, int K_int, const Epilogue &ep,
+                        cudaStream_t st);
 // tcgen05 weight streaming (stream_w.cu): q one code per byte, w packed int4 (bits 4) or int8 (bits 8)
 int launch_stream_w(const void *q, const void *w, int bits, int M, int N, int K_int, const Epilogue &ep,
                     cudaStream_t st);

@@ -56,6 +56,7 @@ struct StreamParams {
   int M, N;
   int nk, nf;                     // k-blocks of the integer part (128 bytes of a W row each) and of the outliers
   int splits;                     // CTAs that share one slab (= cluster size)
+  int prefetch_blocks;            // k-blocks per CTA to prefetch into L2 before waiting for the predecessor
   uint32_t idesc_int, idesc_fp;
   const void *meta, *scale_col, *w_reduced, *bias;
   void *out;
@@ -171,11 +172,13 @@ stream_w_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     tmem_alloc<1>(smem_u32(tmem_slot), SW_TMEM_COLS);
     tmem_relinquish<1>();
   }
-  if (warp == 0 && lane < SW_STAGES && lane < nb) {
-    // ask L2 for the weight tiles of the first blocks while the producer of the token codes still runs
-    const int i = lane;
-    if (i < n_fp) tma_prefetch_2d(&tm_fw, (c0 + i) * 64, n0);
-    else tma_prefetch_2d(&tm_w, (kb_first + i - n_fp) * 128, n0);
+  if (warp == 0) {
+    // ask L2 for this CTA's first weight tiles while the producer of the token codes may still run
+    const int npre = nb < p.prefetch_blocks ? nb : p.prefetch_blocks;
+    for (int i = lane; i < npre; i += 32) {
+      if (i < n_fp) tma_prefetch_2d(&tm_fw, (c0 + i) * 64, n0);
+      else tma_prefetch_2d(&tm_w, (kb_first + i - n_fp) * 128, n0);
+    }
   }
   pdl_wait();      // first global access below
   if (worker) {
@@ -475,6 +478,7 @@ int launch_stream_w(const void *q, const void *w, int bits, int M, int N, int K_
   int splits = 1;
   while (splits < 8 && slabs * splits * 2 <= slots && total / (splits * 2) >= (p.nf > 2 ? p.nf : 2)) splits *= 2;
   p.splits = splits;
+  p.prefetch_blocks = SW_STAGES;   // deeper prefetch was measured slower: the requests delay the first real loads
   p.idesc_int = make_idesc(2, 1, SW_ROWS, SW_TOKENS);
   p.idesc_fp = make_idesc(1, ep.dtype == QUIK_BF16 ? 1 : 0, SW_ROWS, SW_TOKENS);
   p.meta = ep.meta;

@@ -58,12 +58,13 @@ def test_fused_forward_matches_oracle(dtype, M, K, N, F, bits):
     (5, 4232, 300, 72, 4),         # ragged N, K and F
 ])
 def test_small_m_engines_agree(dtype, M, K, N, F, bits):
-    """Few tokens: both weight-streaming engines (tcgen05 with on-chip widening, mma.sync) and the tensor-core
-    GEMM on widened weights give the oracle's result; the integer part is exact in all three."""
+    """Few tokens: the three weight-streaming engines (tcgen05 with on-chip widening; mma.sync fed by direct loads or
+    by a TMA ring) and the tensor-core GEMM on widened weights give the oracle's result; the integer part is exact
+    in all of them."""
     case = make_layer("t", M, K, N, bits, F=F, seed=M + N, device=dev(), dtype=dtype, clip=False)
     outs = {}
     try:
-        for mode in (_lib.SMALL_M_TCGEN05, _lib.SMALL_M_MMA_SYNC, _lib.SMALL_M_OFF, _lib.SMALL_M_AUTO):
+        for mode in (_lib.SMALL_M_TCGEN05, _lib.SMALL_M_MMA_SYNC, _lib.SMALL_M_TMA_MMA, _lib.SMALL_M_OFF, _lib.SMALL_M_AUTO):
             _lib.set_small_m(mode)
             outs[mode] = case.module(case.x.unsqueeze(0))[0].clone()
             again = case.module(case.x.unsqueeze(0))[0]
@@ -80,8 +81,10 @@ def test_small_m_engines_agree(dtype, M, K, N, F, bits):
     agree = 5e-3 if dtype == torch.float16 else 4e-2
     assert rel_rms_err(outs[_lib.SMALL_M_TCGEN05], outs[_lib.SMALL_M_MMA_SYNC]) < agree
     assert rel_rms_err(outs[_lib.SMALL_M_TCGEN05], outs[_lib.SMALL_M_OFF]) < agree
+    assert rel_rms_err(outs[_lib.SMALL_M_TMA_MMA], outs[_lib.SMALL_M_MMA_SYNC]) < agree
     if F == 0:
         assert torch.equal(outs[_lib.SMALL_M_TCGEN05], outs[_lib.SMALL_M_MMA_SYNC])
+        assert torch.equal(outs[_lib.SMALL_M_TMA_MMA], outs[_lib.SMALL_M_MMA_SYNC])
 
 
 @pytest.mark.parametrize("M", [16, 300])
