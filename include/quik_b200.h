@@ -202,6 +202,8 @@ int quik_fused_dequantize(const void *A, const void *B, int bits,
  *                                    (M <= QUIK_SMALL_M_MAX, K_int % 32 == 0).
  * K_int % 16 == 0, F % 8 == 0. */
 #define QUIK_SMALL_M_MAX 16
+/* most tokens the tcgen05 weight-streaming engine takes (q one code per byte, w in storage format) */
+#define QUIK_STREAM_M_MAX 128
 int quik_mixed_linear(const void *q, int q_packed, const void *w, int w_packed,
                       const void *meta, const void *scale_col, const void *w_reduced,
                       const void *fp_x, const void *fp_w, const void *bias, void *out,

@@ -17,7 +17,8 @@ QUIK_OK = 0
 F16, BF16 = 0, 1
 CFG_GEMM_ENGINE, CFG_TILE_N, CFG_SMALL_M, CFG_CTA_PAIR, CFG_PDL = 1, 2, 3, 4, 5
 ENGINE_AUTO, ENGINE_TCGEN05, ENGINE_MMA_SYNC = 0, 1, 2
-SMALL_M_MAX = 16
+SMALL_M_MAX = 16       # most tokens of the mma.sync weight-streaming engines
+STREAM_M_MAX = 128     # most tokens of the tcgen05 weight-streaming engine
 
 _vp, _i, _sz, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_float
 

@@ -334,6 +334,9 @@ int quik_mixed_linear_ld(const void *q, int q_packed, const void *w, int w_packe
     if (engine == 4) return launch_stream_w_mma(q, w, 8, M, N, K_int, ep, st);
     return launch_small_m(q, w, 8, M, N, K_int, ep, st);
   }
+  // 17 to 128 tokens: the tcgen05 streaming engine takes them at the cost of 16 (the tensor-core GEMM would leave
+  // most SMs idle at these sizes)
+  if (bits == 8 && M <= QUIK_STREAM_M_MAX && g_small_m != 0) return launch_stream_w(q, w, 8, M, N, K_int, ep, st);
   return run_int8_gemm(static_cast<const int8_t *>(q), static_cast<const int8_t *>(w), M, N, K_int, ep, st);
 }
 

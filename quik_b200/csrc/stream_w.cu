@@ -36,21 +36,27 @@ namespace {
 constexpr int SW_THREADS = 352;                    // TMA warp, MMA warp, 8 widen/epilogue warps, second MMA warp
 constexpr int SW_ISSUERS = 2;                      // one thread issues a small tcgen05.mma every ~60 ns at best: two share the work
 constexpr int SW_ROWS = 128;                       // weight rows per CTA (the MMA's M)
-constexpr int SW_TOKENS = 16;                      // the MMA's N; tokens beyond M read as zero
-constexpr int SW_STAGES = 5;
 constexpr int SW_W_BYTES = SW_ROWS * 128;          // one k-block of W: 128 bytes per row
-constexpr int SW_X_BYTES = SW_TOKENS * 128;        // one 128-byte k-block of the token operand
-constexpr int SW_STAGE_BYTES = SW_W_BYTES + 2 * SW_X_BYTES;   // int4: 256 codes of W need two token blocks
-constexpr int SW_A_SLOTS = 3;                      // TMEM ring of widened W k-blocks
 constexpr int SW_A_COLS = 64;                      // 256 int8 codes per row = 64 32-bit columns
-constexpr int SW_ACCS = 2;                         // independent s32 accumulators, used in turn and summed at the end:
-                                                   // an MMA this small is bound by the latency of its accumulate
-constexpr int SW_D_INT = SW_A_SLOTS * SW_A_COLS;   // TMEM column of the first s32 accumulator (16 columns each)
-constexpr int SW_D_FP = SW_D_INT + SW_ACCS * SW_TOKENS;   // ... of the f32 accumulator (16 columns)
-constexpr int SW_TMEM_COLS = 256;                  // two CTAs per SM share the 512 columns
-constexpr int SW_RED_BYTES = SW_TOKENS * SW_ROWS * 4;
-constexpr int SW_AUX_BYTES = 1024;
-constexpr size_t SW_SMEM = 1024 + (size_t)SW_STAGES * SW_STAGE_BYTES + SW_RED_BYTES + SW_AUX_BYTES;
+constexpr int SW_ACCS = 2;                         // one s32 accumulator per issuing thread, summed at the end
+constexpr int SW_AUX_BYTES = 2048;
+
+// Sizes that depend on NTOK, the MMA's N: the number of tokens (16, 64 or 128; tokens beyond M read as zero).  A
+// tcgen05.mma costs the same for every N up to 64, so up to 64 tokens ride along with the weight stream for free.
+template <int NTOK> struct SwCfg {
+  static constexpr int X_BYTES = NTOK * 128;                        // one 128-byte k-block of the token operand
+  static constexpr int STAGE_BYTES = SW_W_BYTES + 2 * X_BYTES;      // int4: 256 codes of W need two token blocks
+  static constexpr int CTAS_PER_SM = NTOK == 16 ? 2 : 1;
+  static constexpr int STAGES = NTOK == 128 ? 3 : 5;
+  static constexpr int A_SLOTS = NTOK == 128 ? 2 : 3;               // TMEM ring of widened W k-blocks
+  static constexpr int D_INT = A_SLOTS * SW_A_COLS;                 // TMEM column of the first s32 accumulator
+  static constexpr int D_FP = D_INT + SW_ACCS * NTOK;               // ... of the f32 accumulator
+  static constexpr int TMEM_COLS = NTOK == 16 ? 256 : 512;          // NTOK 16: two CTAs per SM share the 512 columns
+  static constexpr int RED_BYTES = NTOK * SW_ROWS * 4;
+  static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + RED_BYTES + SW_AUX_BYTES;
+  static_assert(D_FP + NTOK <= TMEM_COLS, "TMEM plan");
+  static_assert(SMEM <= 227 * 1024, "shared-memory plan");
+};
 
 struct StreamParams {
   int M, N;
@@ -113,11 +119,15 @@ __device__ __forceinline__ void widen8(uint32_t w, uint32_t &k0123, uint32_t &k4
   k4567 = __byte_perm(even, odd, 0x7362);
 }
 
-template <typename T, int BITS>
-__global__ void __launch_bounds__(SW_THREADS, 2)
+template <typename T, int BITS, int NTOK>
+__global__ void __launch_bounds__(SW_THREADS, SwCfg<NTOK>::CTAS_PER_SM)
 stream_w_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                 const __grid_constant__ CUtensorMap tm_fw, const __grid_constant__ CUtensorMap tm_fx,
                 const StreamParams p) {
+  using Cfg = SwCfg<NTOK>;
+  constexpr int SW_TOKENS = NTOK, SW_X_BYTES = Cfg::X_BYTES, SW_STAGE_BYTES = Cfg::STAGE_BYTES, SW_STAGES = Cfg::STAGES;
+  constexpr int SW_A_SLOTS = Cfg::A_SLOTS, SW_D_INT = Cfg::D_INT, SW_D_FP = Cfg::D_FP, SW_TMEM_COLS = Cfg::TMEM_COLS;
+  constexpr int SW_RED_BYTES = Cfg::RED_BYTES;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   int *red = reinterpret_cast<int *>(tiles + SW_STAGES * SW_STAGE_BYTES);     // [token][row], leader only
@@ -368,58 +378,75 @@ stream_w_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   }
 
   // ================= epilogue (warps 2-9) =================
-  uint32_t acc_i[8], acc_f[8];
+  // Thread (q, lane, h) finishes weight row 32 q + lane for the tokens [h * NTOK / 2, (h + 1) * NTOK / 2), eight at a time.
   bool have = false;
-  const int q = warp & 3, h = (warp - 2) >> 2;      // rows 32q.., tokens 8h..8h+7
+  const int q = warp & 3, h = (warp - 2) >> 2;
+  constexpr int CHUNKS = NTOK / 16;                  // 8-token chunks per thread
+  const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+  auto load_int = [&](int tok0, uint32_t (&acc)[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0;
+    if (n_int > 0) {
+      uint32_t part[8];
+#pragma unroll
+      for (int r = 0; r < SW_ACCS; ++r) {
+        tmem_ld8(tmem_base + lane_base + SW_D_INT + SW_TOKENS * r + tok0, part);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += part[j];
+      }
+    }
+  };
   __syncwarp();
   if (worker) {
     have = mbar_wait(smem_u32(acc_full), 0, abort_flag, p.status) && !*abort_flag;
     have = __all_sync(0xFFFFFFFFu, have);
     tc_fence_after();
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      acc_i[j] = 0;
-      acc_f[j] = 0;
-    }
-    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-    if (have && n_int > 0) {
-      uint32_t part[8];
-#pragma unroll
-      for (int r = 0; r < SW_ACCS; ++r) {
-        tmem_ld8(tmem_base + lane_base + SW_D_INT + SW_TOKENS * r + 8 * h, part);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc_i[j] += part[j];
-      }
-    }
-    if (have && n_fp > 0) tmem_ld8(tmem_base + lane_base + SW_D_FP + 8 * h, acc_f);
-    tmem_ld_wait();
   }
   if (S > 1) {
     cluster_wait();                                  // every CTA of the cluster has started; the buffer is zero
     if (worker && rank != 0 && have) {
       const uint32_t base = map_to_rank(smem_u32(red), 0);
+#pragma unroll 1
+      for (int c = 0; c < CHUNKS; ++c) {
+        const int tok0 = h * (NTOK / 2) + 8 * c;
+        uint32_t acc_i[8];
+        load_int(tok0, acc_i);
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        red_add_cluster(base + (uint32_t)(((8 * h + j) * SW_ROWS + q * 32 + lane) * 4), (int)acc_i[j]);
+        for (int j = 0; j < 8; ++j)
+          red_add_cluster(base + (uint32_t)(((tok0 + j) * SW_ROWS + q * 32 + lane) * 4), (int)acc_i[j]);
+      }
     }
     cluster_arrive();
     cluster_wait();                                  // all partial sums have reached the leader
   }
   if (worker && rank == 0 && have) {
     const int n = n0 + q * 32 + lane;
-    if (n < p.N) {
-      const float scol = Traits<T>::to_float(ep_scol), wred = Traits<T>::to_float(ep_wred), bias = Traits<T>::to_float(ep_bias);
-      T *out = static_cast<T *>(p.out);
+    const float scol = Traits<T>::to_float(ep_scol), wred = Traits<T>::to_float(ep_wred), bias = Traits<T>::to_float(ep_bias);
+    T *out = static_cast<T *>(p.out);
+#pragma unroll 1
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int tok0 = h * (NTOK / 2) + 8 * c;
+      if (tok0 >= p.M) break;                        // warp-uniform
+      uint32_t acc_i[8], acc_f[8];
+      load_int(tok0, acc_i);                         // tcgen05.ld is warp-collective: all lanes, also rows beyond N
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int m = 8 * h + j;
-        if (m < p.M) {
-          int acc = (int)acc_i[j];
-          if (S > 1) acc += red[m * SW_ROWS + q * 32 + lane];
-          if (BITS == 4) acc >>= 4;                  // the weights carried a factor 16; the quotient is exact
-          const float add = fmaf(s_zs[m], wred, __uint_as_float(acc_f[j]) + bias);
-          out[(size_t)m * p.ldo + n] = Traits<T>::from_float(fmaf((float)acc, s_srow[m] * scol, add));
+      for (int j = 0; j < 8; ++j) acc_f[j] = 0;
+      if (n_fp > 0) {
+        tmem_ld8(tmem_base + lane_base + SW_D_FP + tok0, acc_f);
+        tmem_ld_wait();
+      }
+      if (n < p.N) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int m = tok0 + j;
+          if (m < p.M) {
+            int acc = (int)acc_i[j];
+            if (S > 1) acc += red[m * SW_ROWS + q * 32 + lane];
+            if (BITS == 4) acc >>= 4;                // the weights carried a factor 16; the quotient is exact
+            const float add = fmaf(s_zs[m], wred, __uint_as_float(acc_f[j]) + bias);
+            out[(size_t)m * p.ldo + n] = Traits<T>::from_float(fmaf((float)acc, s_srow[m] * scol, add));
+          }
         }
       }
     }
@@ -438,16 +465,16 @@ stream_w_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   }
 }
 
-template <typename T, int BITS>
+template <typename T, int BITS, int NTOK>
 int launch_t(const CUtensorMap &tw, const CUtensorMap &tx, const CUtensorMap &tfw, const CUtensorMap &tfx,
              const StreamParams &p, int slabs, cudaStream_t st) {
-  auto kern = stream_w_kernel<T, BITS>;
+  auto kern = stream_w_kernel<T, BITS, NTOK>;
   static bool configured = false;
   if (!configured) {
-    QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SW_SMEM));
+    QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SwCfg<NTOK>::SMEM));
     configured = true;
   }
-  LaunchCfg lc(dim3(slabs * p.splits), dim3(SW_THREADS), SW_SMEM, st, p.splits);
+  LaunchCfg lc(dim3(slabs * p.splits), dim3(SW_THREADS), SwCfg<NTOK>::SMEM, st, p.splits);
   QUIK_CUDA_TRY(cudaLaunchKernelEx(&lc.cfg, kern, tw, tx, tfw, tfx, p));
   return check_launch("stream_w_kernel");
 }
@@ -458,13 +485,16 @@ int launch_t(const CUtensorMap &tw, const CUtensorMap &tx, const CUtensorMap &tf
 int launch_stream_w(const void *q, const void *w, int bits, int M, int N, int K_int, const Epilogue &ep,
                     cudaStream_t st) {
   if (M == 0 || N == 0) return QUIK_OK;
-  if (M > SW_TOKENS) return QUIK_ERR_UNSUPPORTED;
+  if (M > QUIK_STREAM_M_MAX) return QUIK_ERR_UNSUPPORTED;
   if (K_int <= 0 || K_int % (bits == 4 ? 32 : 16) != 0) return QUIK_ERR_SHAPE;
   if (!aligned16(q) || !aligned16(w)) return QUIK_ERR_ALIGN;
   const bool has_fp = ep.fp_a != nullptr && ep.F > 0;
   if (has_fp && (ep.F % 8 != 0 || !aligned16(ep.fp_a) || !aligned16(ep.fp_b))) return QUIK_ERR_ALIGN;
   if (ep.meta == nullptr || ep.w_reduced == nullptr || ep.y != nullptr) return QUIK_ERR_UNSUPPORTED;
 
+  const int ntok = M <= 16 ? 16 : (M <= 64 ? 64 : 128);          // the MMA's N
+  const int ctas_per_sm = ntok == 16 ? 2 : 1;
+  const int stages = ntok == 128 ? 3 : 5;
   StreamParams p{};
   p.M = M;
   p.N = N;
@@ -472,15 +502,15 @@ int launch_stream_w(const void *q, const void *w, int bits, int M, int N, int K_
   p.nk = (w_row_bytes + 127) / 128;
   p.nf = has_fp ? (ep.F + 63) / 64 : 0;
   const int slabs = (N + SW_ROWS - 1) / SW_ROWS;
-  // Split K over a cluster while all CTAs still fit on the GPU at once (two per SM), every CTA keeps at
-  // least two k-blocks and the outlier blocks all fall to the first CTA.
-  const int total = p.nk + p.nf, slots = 2 * num_sms();
+  // Split K over a cluster while all CTAs still fit on the GPU at once, every CTA keeps at least two k-blocks and
+  // the outlier blocks all fall to the first CTA.
+  const int total = p.nk + p.nf, slots = ctas_per_sm * num_sms();
   int splits = 1;
   while (splits < 8 && slabs * splits * 2 <= slots && total / (splits * 2) >= (p.nf > 2 ? p.nf : 2)) splits *= 2;
   p.splits = splits;
-  p.prefetch_blocks = SW_STAGES;   // deeper prefetch was measured slower: the requests delay the first real loads
-  p.idesc_int = make_idesc(2, 1, SW_ROWS, SW_TOKENS);
-  p.idesc_fp = make_idesc(1, ep.dtype == QUIK_BF16 ? 1 : 0, SW_ROWS, SW_TOKENS);
+  p.prefetch_blocks = stages;      // deeper prefetch was measured slower: the requests delay the first real loads
+  p.idesc_int = make_idesc(2, 1, SW_ROWS, ntok);
+  p.idesc_fp = make_idesc(1, ep.dtype == QUIK_BF16 ? 1 : 0, SW_ROWS, ntok);
   p.meta = ep.meta;
   p.scale_col = ep.scale_col;
   p.w_reduced = ep.w_reduced;
@@ -495,20 +525,28 @@ int launch_stream_w(const void *q, const void *w, int bits, int M, int N, int K_
   CUtensorMap tw, tx, tfw, tfx;
   int rc;
   if ((rc = make_tmap(&tw, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, w_row_bytes, SW_ROWS)) != QUIK_OK) return rc;
-  if ((rc = make_tmap(&tx, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K_int, SW_TOKENS)) != QUIK_OK) return rc;
+  if ((rc = make_tmap(&tx, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K_int, ntok)) != QUIK_OK) return rc;
   if (has_fp) {
     const CUtensorMapDataType fdt = ep.dtype == QUIK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     if ((rc = make_tmap(&tfw, ep.fp_b, fdt, 2, N, ep.F, SW_ROWS)) != QUIK_OK) return rc;
-    if ((rc = make_tmap(&tfx, ep.fp_a, fdt, 2, M, ep.F, SW_TOKENS)) != QUIK_OK) return rc;
+    if ((rc = make_tmap(&tfx, ep.fp_a, fdt, 2, M, ep.F, ntok)) != QUIK_OK) return rc;
   } else {
     tfw = tw;
     tfx = tx;
   }
-  if (ep.dtype == QUIK_BF16)
-    return bits == 4 ? launch_t<__nv_bfloat16, 4>(tw, tx, tfw, tfx, p, slabs, st)
-                     : launch_t<__nv_bfloat16, 8>(tw, tx, tfw, tfx, p, slabs, st);
-  return bits == 4 ? launch_t<__half, 4>(tw, tx, tfw, tfx, p, slabs, st)
-                   : launch_t<__half, 8>(tw, tx, tfw, tfx, p, slabs, st);
+#define QUIK_SW(T, B)                                                                    \
+  do {                                                                                   \
+    if (ntok == 16) return launch_t<T, B, 16>(tw, tx, tfw, tfx, p, slabs, st);           \
+    if (ntok == 64) return launch_t<T, B, 64>(tw, tx, tfw, tfx, p, slabs, st);           \
+    return launch_t<T, B, 128>(tw, tx, tfw, tfx, p, slabs, st);                          \
+  } while (0)
+  if (ep.dtype == QUIK_BF16) {
+    if (bits == 4) QUIK_SW(__nv_bfloat16, 4);
+    QUIK_SW(__nv_bfloat16, 8);
+  }
+  if (bits == 4) QUIK_SW(__half, 4);
+  QUIK_SW(__half, 8);
+#undef QUIK_SW
 }
 
 }  // namespace quik

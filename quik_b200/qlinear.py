@@ -136,8 +136,9 @@ class MixedQLinear(torch.nn.Module):
         # Above SMALL_M_MAX tokens: tensor-core GEMM on codes widened to one per byte (both operands).  Below:
         # weight streaming, the weights stay packed; the tcgen05 engine takes the token codes one per byte, the
         # mma.sync engine (the default for 4-bit layers: faster on the layer sizes measured) packed like the weights.
-        stream = M <= _lib.SMALL_M_MAX and _lib.small_m_mode != _lib.SMALL_M_OFF
-        wide = not (stream and _lib.small_m_mode != _lib.SMALL_M_TCGEN05)
+        # From 17 to STREAM_M_MAX tokens only the tcgen05 streaming engine applies.
+        stream = M <= _lib.STREAM_M_MAX and _lib.small_m_mode != _lib.SMALL_M_OFF
+        wide = not (stream and M <= _lib.SMALL_M_MAX and _lib.small_m_mode != _lib.SMALL_M_TCGEN05)
         if shared_input.qint_x is None:
             i16, f16 = self._idx16()
             shared_input.qint_x, shared_input.meta, shared_input.fp_x = asymmetric.quantize_u16(
