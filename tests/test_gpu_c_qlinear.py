@@ -87,6 +87,27 @@ def test_small_m_engines_agree(dtype, M, K, N, F, bits):
         assert torch.equal(outs[_lib.SMALL_M_TMA_MMA], outs[_lib.SMALL_M_MMA_SYNC])
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M", [17, 33, 64, 65, 100, 128])
+@pytest.mark.parametrize("K,N,F,bits", [(4352, 4096, 256, 4), (11264, 520, 256, 8), (1056, 300, 32, 4)])
+def test_streaming_engine_up_to_128_tokens(dtype, M, K, N, F, bits):
+    """17 to 128 tokens run on the tcgen05 weight-streaming engine (token operand of 64 or 128 rows, weights in
+    storage format); same result as the tiled tensor-core GEMM on widened weights, and the oracle's."""
+    case = make_layer("t", M, K, N, bits, F=F, seed=M + N, device=dev(), dtype=dtype, clip=False)
+    try:
+        out = case.module(case.x.unsqueeze(0))[0].clone()
+        again = case.module(case.x.unsqueeze(0))[0]
+        _lib.set_small_m(_lib.SMALL_M_OFF)
+        tiled = case.module(case.x.unsqueeze(0))[0].clone()
+    finally:
+        _lib.set_small_m(_lib.SMALL_M_AUTO)
+    assert_device_clean()
+    assert torch.equal(out, again)
+    tol = TOL_RMS if dtype == torch.float16 else 4e-2
+    assert rel_rms_err(out.cpu(), _oracle_out(case, round_y=False)) < tol
+    assert rel_rms_err(out, tiled) < (5e-3 if dtype == torch.float16 else 4e-2)
+
+
 @pytest.mark.parametrize("M", [16, 300])
 def test_dependent_launch_matches_stream_order(M):
     """A chain of layers (each output feeds the next quantizer) with kernels launched as programmatic dependents
