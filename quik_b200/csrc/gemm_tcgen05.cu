@@ -9,16 +9,16 @@
 //                                                                                asymmetric.cu:134-146
 // or stores acc_i as int32 (mode 0).
 //
-// Structure (one persistent CTA per SM, 192 threads):
+// Structure (one persistent CTA per SM or one CTA pair per two SMs, 320 threads per CTA):
 //   warp 0    TMA producer: cp.async.bulk.tensor.2d loads of the A / B k-blocks (128 bytes of K
 //             per row, 128B swizzle) into a ring of shared-memory stages, completion on mbarriers.
-//   warp 1    allocates TMEM; one elected lane issues tcgen05.mma (M=128, N=BLOCK_N, K=32 bytes)
-//             from shared-memory descriptors and commits each stage back to the producer.
-//   warps 2-5 epilogue: tcgen05.ld the accumulators (32 lanes x 32 columns per warp and step),
-//             apply the dequantize arithmetic in fp32 and store 16-byte vectors.
-// Outlier k-blocks (64 fp16 values = 128 bytes per row) travel through the same ring before the
-// integer k-blocks of a tile.  With BLOCK_N = 256 the integer-only kernel double-buffers the
-// accumulator (2 x 256 TMEM columns) so the epilogue of tile i overlaps the MMAs of tile i+1.
+//   warp 1    allocates TMEM; one elected lane issues tcgen05.mma (M=128 or 256, N=BLOCK_N, K=32
+//             bytes) from shared-memory descriptors and commits each stage back to the producer.
+//   warps 2-9 epilogue: tcgen05.ld the accumulators (32 lanes x 32 columns per warp and step),
+//             apply the dequantize arithmetic in fp32 and store through a shared-memory transpose.
+// Outlier k-blocks (64 fp16 values = 128 bytes per row) travel through the same ring as the integer
+// k-blocks; TMEM holds two accumulator regions so the epilogue of tile i overlaps the MMAs of tile
+// i+1 (schedule in the comment above the kernel).
 // Every wait is bounded: when a limit is hit the kernel records it in a device status word,
 // all roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda.h>

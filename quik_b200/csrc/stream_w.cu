@@ -1,21 +1,21 @@
-// Weight-streaming fused layer for few tokens (M <= 16) on the tcgen05 tensor cores.
+// Weight-streaming fused layer for few tokens (M <= 128) on the tcgen05 tensor cores.
 //
-// With at most 16 tokens the layer (QUIK experiments/qlinear.py:122-145) is bound by reading the weights
+// With few tokens the layer (QUIK experiments/qlinear.py:122-145) is bound by reading the weights
 // once from HBM, so the kernel is built around the weight stream and keeps the weights in their storage
 // format: packed int4 (two codes per byte, low nibble first, QUIK include/int4.h:78-98) or int8.
 //
 // The product is computed transposed, out^T[n, m] = sum_k W[n, k] * Xq[m, k]: 128 weight rows are the
-// M = 128 operand of tcgen05.mma, the (zero-padded) 16 tokens its N = 16 operand, so one instruction
-// consumes 128 x 32 weight codes.  Per CTA (one 128-row slab of W, one share of K):
+// M = 128 operand of tcgen05.mma, the tokens (zero-padded to NTOK = 16, 64 or 128) its N operand, so one
+// instruction consumes 128 x 32 weight codes.  Per CTA (one 128-row slab of W, one share of K):
 //   warp 0      TMA producer: k-blocks of W (128 rows x 128 bytes, 128B swizzle) and of the token codes /
-//               outlier values (16 rows x 128 bytes) into a ring of shared-memory stages.
+//               outlier values (NTOK rows x 128 bytes) into a ring of shared-memory stages.
 //   warps 2-9   int4 only: each thread takes 64 packed bytes of "its" weight row from shared memory, widens
 //               the 128 nibbles to signed bytes that carry 16 x the code (shift, two masks and two byte
 //               permutes per 8 codes, natural k order) and writes them with tcgen05.st into a ring of TMEM
 //               slots: the widened weights never touch shared or global memory.
-//   warp 1      one lane issues tcgen05.mma kind::i8 with A read from TMEM (int4) or from the shared-memory
-//               stage (int8), and kind::f16 for the outlier columns, B always from shared memory;
-//               accumulators (s32 and f32, 16 columns each) live in TMEM.
+//   warps 1,10  one lane each issues every second tcgen05.mma of a k-block (kind::i8 with A read from TMEM (int4)
+//               or from the shared-memory stage (int8), B always from shared memory) into its own s32 accumulator;
+//               warp 1 also issues kind::f16 for the outlier columns.  Accumulators (NTOK columns each) live in TMEM.
 //   warps 2-9   epilogue: tcgen05.ld of the accumulators, split-K reduction, dequantize arithmetic of
 //               QUIK src/asymmetric/asymmetric.cu:134-146, stores of out[m, n] (64 contiguous bytes per warp
 //               and token).
@@ -139,8 +139,8 @@ stream_w_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   uint64_t *acc_full = a_empty + SW_A_SLOTS;                    // all MMAs of this CTA complete
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-  float *s_srow = reinterpret_cast<float *>(aux + 256);         // [16] token scale
-  float *s_zs = s_srow + SW_TOKENS;                             // [16] zero + shift * scale
+  float *s_srow = reinterpret_cast<float *>(aux + 256);         // [NTOK] token scale
+  float *s_zs = s_srow + SW_TOKENS;                             // [NTOK] zero + shift * scale
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool worker = warp >= 2 && warp < 10;                     // widening + epilogue warps
