@@ -17,7 +17,7 @@ namespace quik {
 
 namespace {
 
-constexpr int kQuantThreads = 256;
+constexpr int kQuantThreads = 256;     // threads per row; few rows use twice as many
 
 template <typename T> __device__ __forceinline__ T t_sub(T a, T b) { return __hsub(a, b); }
 template <typename T> __device__ __forceinline__ T t_div(T a, T b) { return __hdiv(a, b); }
@@ -83,14 +83,14 @@ __device__ __forceinline__ void emit_codes(const uint32_t (&c)[4], uint32_t &w0,
 // IdxT: int64_t (reference ABI) or uint16_t (layer-cached ids).
 // NC = register-cached chunks per thread (6 covers rows of up to 12288 integer columns; longer rows gather twice)
 
-template <typename T, int BITS, bool WIDE, typename IdxT, int NC>
-__global__ void __launch_bounds__(kQuantThreads)
+template <typename T, int BITS, bool WIDE, typename IdxT, int NC, int NTHR>
+__global__ void __launch_bounds__(NTHR)
 asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int_idx,
                          const IdxT *__restrict__ fp_idx, int rows, int cols, int num_int, int num_fp,
                          uint8_t *__restrict__ dst, T *__restrict__ meta, T *__restrict__ fp_x,
                          int vec_load, int vec_store, int vec_ids, int nbuf) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ float s_red[2][kQuantThreads / 32];
+  __shared__ float s_red[2][NTHR / 32];
   const int cols_pad = (cols + 7) & ~7;
   T *s_buf = reinterpret_cast<T *>(smem_raw);          // two row buffers: the next row loads while this one is used
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -101,7 +101,7 @@ asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int
   auto prefetch_row = [&](int r, int buf) {
     const unsigned sbase = (unsigned)__cvta_generic_to_shared(s_buf + (size_t)buf * cols_pad);
     const uint4 *g = reinterpret_cast<const uint4 *>(src + (size_t)r * cols);
-    for (int i = tid; i < (cols >> 3); i += kQuantThreads)
+    for (int i = tid; i < (cols >> 3); i += NTHR)
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sbase + i * 16), "l"(g + i));
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
@@ -124,7 +124,7 @@ asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int
   uint32_t ids[NC][4];
 #pragma unroll
   for (int it = 0; it < NC; ++it) {
-    const int c = tid + kQuantThreads * it;
+    const int c = tid + NTHR * it;
     if (c < num_chunks) load_ids(c, ids[it]);
   }
 
@@ -144,7 +144,7 @@ asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int
   } else {
     __syncthreads();
     const T *row = src + (size_t)r * cols;
-    for (int i = tid; i < cols; i += kQuantThreads) s_row[i] = row[i];
+    for (int i = tid; i < cols; i += NTHR) s_row[i] = row[i];
     __syncthreads();
   }
 
@@ -177,13 +177,13 @@ asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int
   };
 #pragma unroll
   for (int it = 0; it < NC; ++it) {
-    const int c = tid + kQuantThreads * it;
+    const int c = tid + NTHR * it;
     if (c < num_chunks) {
       gather(ids[it], pr[it]);
       minmax(pr[it]);
     }
   }
-  for (int c = tid + kQuantThreads * NC; c < num_chunks; c += kQuantThreads) {   // very long rows
+  for (int c = tid + NTHR * NC; c < num_chunks; c += NTHR) {   // very long rows
     uint32_t w[4], p[4];
     load_ids(c, w);
     gather(w, p);
@@ -197,7 +197,7 @@ asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int
   }
   __syncthreads();
 #pragma unroll
-  for (int w = 0; w < kQuantThreads / 32; ++w) {
+  for (int w = 0; w < NTHR / 32; ++w) {
     mx = fmaxf(mx, s_red[0][w]);
     mn = fminf(mn, s_red[1][w]);
   }
@@ -259,10 +259,10 @@ asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int
   };
 #pragma unroll
   for (int it = 0; it < NC; ++it) {
-    const int c = tid + kQuantThreads * it;
+    const int c = tid + NTHR * it;
     if (c < num_chunks) emit(c, pr[it]);
   }
-  for (int c = tid + kQuantThreads * NC; c < num_chunks; c += kQuantThreads) {
+  for (int c = tid + NTHR * NC; c < num_chunks; c += NTHR) {
     uint32_t w[4], p[4];
     load_ids(c, w);
     gather(w, p);
@@ -271,18 +271,18 @@ asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int
 
   // ---- outlier columns, verbatim
   T *frow = fp_x + (size_t)r * num_fp;
-  for (int j = tid; j < num_fp; j += kQuantThreads) frow[j] = s_row[(int)fp_idx[j]];
+  for (int j = tid; j < num_fp; j += NTHR) frow[j] = s_row[(int)fp_idx[j]];
   }
 }
 
-template <typename T, int BITS, bool WIDE, typename IdxT, int NC>
+template <typename T, int BITS, bool WIDE, typename IdxT, int NC, int NTHR>
 int launch_asym_rows_nc(const void *src, int rows, int cols, const void *int_idx, int num_int,
                      const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x, cudaStream_t st) {
   const size_t row_bytes = (size_t)((cols + 7) & ~7) * sizeof(T);
   const int nbuf = 2 * row_bytes <= 200 * 1024 ? 2 : 1;
   const size_t smem = nbuf * row_bytes;
   if (smem > 200 * 1024) return QUIK_ERR_UNSUPPORTED;
-  auto kern = asym_quantize_row_kernel<T, BITS, WIDE, IdxT, NC>;
+  auto kern = asym_quantize_row_kernel<T, BITS, WIDE, IdxT, NC, NTHR>;
   // attribute and occupancy are looked up once per (instantiation, shared-memory size)
   static size_t cached_smem = 0;
   static int cached_per_sm = 0;
@@ -290,7 +290,7 @@ int launch_asym_rows_nc(const void *src, int rows, int cols, const void *int_idx
     if (smem > 48 * 1024)
       QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int occ = 0;
-    QUIK_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kQuantThreads, smem));
+    QUIK_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NTHR, smem));
     if (occ < 1) return QUIK_ERR_UNSUPPORTED;
     cached_smem = smem;
     cached_per_sm = occ;
@@ -300,7 +300,7 @@ int launch_asym_rows_nc(const void *src, int rows, int cols, const void *int_idx
   const bool packed = (BITS == 4 && !WIDE);
   const int vec_store = (num_int % 8 == 0) && ((reinterpret_cast<uintptr_t>(dst) & (packed ? 3u : 7u)) == 0);
   const int vec_ids = sizeof(IdxT) == 2 && (num_int % 8 == 0) && aligned16(int_idx);
-  LaunchCfg lc(dim3(grid), dim3(kQuantThreads), smem, st);
+  LaunchCfg lc(dim3(grid), dim3(NTHR), smem, st);
   QUIK_CUDA_TRY(cudaLaunchKernelEx(&lc.cfg, kern, static_cast<const T *>(src), static_cast<const IdxT *>(int_idx),
                                    static_cast<const IdxT *>(fp_idx), rows, cols, num_int, num_fp,
                                    static_cast<uint8_t *>(dst), static_cast<T *>(meta), static_cast<T *>(fp_x),
@@ -308,15 +308,26 @@ int launch_asym_rows_nc(const void *src, int rows, int cols, const void *int_idx
   return check_launch("asym_quantize_row_kernel");
 }
 
+template <typename T, int BITS, bool WIDE, typename IdxT, int NTHR>
+int launch_asym_rows_thr(const void *src, int rows, int cols, const void *int_idx, int num_int,
+                         const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x, cudaStream_t st) {
+  const int per_thread = (((num_int + 7) >> 3) + NTHR - 1) / NTHR;
+  if (per_thread <= 2)
+    return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 2, NTHR>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+  if (per_thread <= 4)
+    return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 4, NTHR>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+  return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 6, NTHR>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+}
+
+// With fewer rows than SMs the row's latency is all there is: 512 threads per row (measured 2.6 / 3.4 us against
+// 2.9 / 4.1 us for 16 rows of 4096 / 11008 columns); with many rows 256 threads give more rows in flight per SM
+// (10.9 / 21 us against 13.9 / 25.8 us for 2048 rows).
 template <typename T, int BITS, bool WIDE, typename IdxT>
 int launch_asym_rows(const void *src, int rows, int cols, const void *int_idx, int num_int,
                      const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x, cudaStream_t st) {
-  const int per_thread = (((num_int + 7) >> 3) + kQuantThreads - 1) / kQuantThreads;
-  if (per_thread <= 2)
-    return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 2>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
-  if (per_thread <= 4)
-    return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 4>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
-  return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 6>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+  if (rows <= num_sms())
+    return launch_asym_rows_thr<T, BITS, WIDE, IdxT, 2 * kQuantThreads>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+  return launch_asym_rows_thr<T, BITS, WIDE, IdxT, kQuantThreads>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
 }
 
 template <typename T, typename IdxT>

@@ -137,7 +137,9 @@ class MixedQLinear(torch.nn.Module):
         # weight streaming, the weights stay packed; the tcgen05 engine takes the token codes one per byte, the
         # mma.sync engine (the default for 4-bit layers: faster on the layer sizes measured) packed like the weights.
         # From 17 to STREAM_M_MAX tokens only the tcgen05 streaming engine applies.
-        stream = M <= _lib.STREAM_M_MAX and _lib.small_m_mode != _lib.SMALL_M_OFF
+        # (a packed 4-bit row must be a multiple of 16 bytes for the streaming engines; otherwise the tiled GEMM)
+        stream = M <= _lib.STREAM_M_MAX and _lib.small_m_mode != _lib.SMALL_M_OFF \
+            and (self.bits == 8 or self.int_features_num % 32 == 0)
         wide = not (stream and M <= _lib.SMALL_M_MAX and _lib.small_m_mode != _lib.SMALL_M_TCGEN05)
         if shared_input.qint_x is None:
             i16, f16 = self._idx16()

@@ -29,6 +29,7 @@ def _oracle_out(case, round_y):
     (1, 4096, 512, 256, 4), (16, 4096, 264, 256, 4), (16, 1024, 128, 0, 8), (7, 11008, 256, 256, 8),
     (17, 4096, 512, 256, 4), (129, 4096, 520, 256, 4), (256, 1024, 384, 0, 4), (128, 11008, 256, 256, 8),
     (2048, 4096, 1024, 256, 4), (300, 8192, 1024, 1024, 4), (64, 96, 40, 32, 4),
+    (40, 112, 24, 32, 4), (9, 112, 24, 32, 4),      # 80 integer columns: packed rows of 40 bytes, tiled GEMM at any M
 ])
 def test_fused_forward_matches_oracle(dtype, M, K, N, F, bits):
     case = make_layer("t", M, K, N, bits, F=F, seed=M + N, device=dev(), dtype=dtype, clip=False)
