@@ -367,12 +367,16 @@ def main():
         d2h = sum(t.numel() * t.element_size() for t in ho)
 
         if world > 1:
+            # every rank uploads the (replicated) activations; the assembled result is read back once, by rank 0
+            h2d *= world
+
             def e2e_step():
                 for i, layer in enumerate(layers):
                     dx[i].copy_(hx[i], non_blocking=True)
                     out = layer(dx[i].unsqueeze(0))
                     layer.wait()
-                    ho[i].copy_(out, non_blocking=True)
+                    if rank == 0:
+                        ho[i].copy_(out, non_blocking=True)
         else:
             # Host side of a serving loop: uploads, layers and downloads run on three streams, chained per layer by
             # events, so the two PCIe directions and the kernels overlap (every step still uploads all its inputs and
