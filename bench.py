@@ -471,7 +471,7 @@ def main():
                 "cpu_baseline": cpu_base, "e2e": e2e, "gpu_launches": 2 * len(shapes) * args.steps, "clocks": clocks,
                 "launch_mode": "cuda graph replay" if graph is not None else "eager", "eager_ms_per_step": eager_ms_step,
                 "decoder_block": block,
-                "frac_of_int8_peak_whole_step": value / int8_peak}
+                "frac_of_int8_peak_whole_step": value / (int8_peak * world)}
         print(json.dumps(line), flush=True)
     if world > 1:
         # leave without tearing the communicators down: graph-captured collectives and symmetric-memory
