@@ -366,42 +366,37 @@ def main():
         h2d = sum(t.numel() * t.element_size() for t in hx)
         d2h = sum(t.numel() * t.element_size() for t in ho)
 
+        # Host side of a serving loop: uploads, layers and downloads run on three streams, chained per layer by
+        # events, so the two PCIe directions and the kernels overlap (every step still uploads all its inputs and
+        # downloads all its outputs inside the timed region).  Tensor parallel: every rank uploads the (replicated)
+        # activations; the assembled result is read back once, by rank 0.
         if world > 1:
-            # every rank uploads the (replicated) activations; the assembled result is read back once, by rank 0
             h2d *= world
-
-            def e2e_step():
-                for i, layer in enumerate(layers):
-                    dx[i].copy_(hx[i], non_blocking=True)
-                    out = layer(dx[i].unsqueeze(0))
-                    layer.wait()
-                    if rank == 0:
-                        ho[i].copy_(out, non_blocking=True)
-        else:
-            # Host side of a serving loop: uploads, layers and downloads run on three streams, chained per layer by
-            # events, so the two PCIe directions and the kernels overlap (every step still uploads all its inputs and
-            # downloads all its outputs inside the timed region).
-            s_comp = torch.cuda.current_stream()
-            s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-            dout = [torch.empty((M, c.N), dtype=torch.float16, device=dev) for c in cases]
-            ev_in = [torch.cuda.Event() for _ in cases]
-            ev_done = [torch.cuda.Event() for _ in cases]
-            ev_out = [torch.cuda.Event() for _ in cases]
-            for i, layer in enumerate(layers):
+        s_comp = torch.cuda.current_stream()
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        dout = [torch.empty((M, c.N), dtype=torch.float16, device=dev) for c in cases] if world == 1 else None
+        ev_in = [torch.cuda.Event() for _ in cases]
+        ev_done = [torch.cuda.Event() for _ in cases]
+        ev_out = [torch.cuda.Event() for _ in cases]
+        for i, layer in enumerate(layers):
+            if world == 1:
                 layer.out_buffer = dout[i]
-                ev_done[i].record(s_comp)
-                ev_out[i].record(s_out)
+            ev_done[i].record(s_comp)
+            ev_out[i].record(s_out)
 
-            def e2e_step():
-                for i, layer in enumerate(layers):
-                    s_in.wait_event(ev_done[i])            # the layer's previous input has been consumed
-                    with torch.cuda.stream(s_in):
-                        dx[i].copy_(hx[i], non_blocking=True)
-                        ev_in[i].record(s_in)
-                    s_comp.wait_event(ev_in[i])
-                    s_comp.wait_event(ev_out[i])           # the layer's previous output has been downloaded
-                    out = layer(dx[i].unsqueeze(0))
-                    ev_done[i].record(s_comp)
+        def e2e_step():
+            for i, layer in enumerate(layers):
+                s_in.wait_event(ev_done[i])            # the layer's previous input has been consumed
+                with torch.cuda.stream(s_in):
+                    dx[i].copy_(hx[i], non_blocking=True)
+                    ev_in[i].record(s_in)
+                s_comp.wait_event(ev_in[i])
+                s_comp.wait_event(ev_out[i])           # the layer's previous output has been downloaded
+                out = layer(dx[i].unsqueeze(0))
+                if world > 1:
+                    layer.wait()                       # the peers' column ranges have arrived
+                ev_done[i].record(s_comp)
+                if rank == 0:
                     s_out.wait_event(ev_done[i])
                     with torch.cuda.stream(s_out):
                         ho[i].copy_(out, non_blocking=True)
@@ -415,8 +410,7 @@ def main():
         a.record()
         for _ in range(e_steps):
             e2e_step()
-        if world == 1:
-            torch.cuda.current_stream().wait_stream(s_out)     # the last download is inside the timed region
+        torch.cuda.current_stream().wait_stream(s_out)         # the last download is inside the timed region
         b.record()
         sync_all()
         if world == 1:
