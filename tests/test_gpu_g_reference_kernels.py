@@ -1,0 +1,149 @@
+"""GPU parity against the reference's OWN CUDA kernels on the same inputs.
+
+oracle/build_ref.py compiles the QUIK reference's quantize / quantizeOld / find_meta / dequantize and symmetric
+quantize / dequantize kernels unmodified from the reference checkout (src/asymmetric/asymmetric.cu,
+src/symmetric/symmetric.cu) into oracle/_ref/.  These tests run them next to this repository's kernels and demand
+identical bytes.  They are skipped when that library is absent (it is built where the reference checkout is
+available and travels with the repository's other built files).
+
+Shapes respect what the reference kernels assume: at least 1024 elements (its block size then is the power of two its
+tree reduction needs), at least 1024 columns for the fused quantizer (one row per block: its blocks do not
+synchronise between rows), power-of-two columns for find_meta, an even element count for dequantize.
+"""
+import pytest
+import torch
+
+from oracle import build_ref
+from tests.gpu_util import assert_device_clean, dev
+
+pytestmark = pytest.mark.gpu
+
+_ref = None
+
+
+def ref_ops():
+    global _ref
+    if _ref is None:
+        _ref = build_ref.load() or False
+    if not _ref:
+        pytest.skip("oracle/_ref (reference kernels) not built")
+    return _ref
+
+
+def _indices(cols, nfp, order, seed):
+    g = torch.Generator().manual_seed(seed)
+    fp = torch.randperm(cols, generator=g)[:nfp]
+    ints = torch.arange(cols)
+    ints = ints[~torch.isin(ints, fp)]
+    if order == "ascending":
+        fp = fp.sort()[0]
+    else:
+        ints = ints[torch.randperm(ints.numel(), generator=g)]
+    return ints, fp
+
+
+def _activations(rows, cols, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, cols, generator=g)
+    x[:, torch.randperm(cols, generator=g)[: max(1, cols // 16)]] *= 20.0
+    return x.to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("rows,cols,nfp,order", [
+    (16, 4352, 256, "ascending"), (129, 11264, 256, "ascending"), (2048, 4352, 256, "shuffled"),
+    (7, 1024, 0, "ascending"), (33, 8192 + 1024, 1024, "shuffled"), (1, 2048, 64, "ascending"),
+])
+def test_asym_quantize_equals_reference_kernel(dtype, bits, rows, cols, nfp, order):
+    """quik.asymmetric.quantize (asymmetric.cu:340-584): codes, meta and outlier columns, byte for byte."""
+    import quik
+    ref = ref_ops()
+    x = _activations(rows, cols, dtype, rows + cols + bits).to(dev())
+    ints, fp = _indices(cols, nfp, order, cols + nfp)
+    ints, fp = ints.to(dev()), fp.to(dev())
+    q_ref, meta_ref, fp_ref = ref.asym_quantize(x, ints, fp, bits)
+    torch.cuda.synchronize()
+    q, meta, fp_x = quik.asymmetric.quantize(x, ints, fp, bits)
+    torch.cuda.synchronize()
+    assert q.dtype == q_ref.dtype and q.shape == q_ref.shape
+    assert torch.equal(meta, meta_ref)
+    assert torch.equal(fp_x, fp_ref)
+    assert torch.equal(q, q_ref)
+    # the layer path's variant (16-bit ids, one code per byte) carries the same codes
+    from quik_b200.qlinear import _to_u16
+    qw, meta_w, _ = quik.asymmetric.quantize_u16(x, _to_u16(ints), _to_u16(fp), bits, True)
+    assert torch.equal(meta_w, meta_ref)
+    if bits == 8:
+        assert torch.equal(qw, q_ref)
+    else:
+        lo = ((q_ref & 0xF).to(torch.int8) ^ 8) - 8
+        hi = ((q_ref >> 4).to(torch.int8) ^ 8) - 8
+        assert torch.equal(qw, torch.stack([lo, hi], dim=2).reshape(rows, -1))
+    assert_device_clean()
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("rows,cols", [(37, 1024), (128, 4096), (2, 512)])
+def test_find_meta_and_quantize_old_equal_reference_kernels(bits, rows, cols):
+    import quik
+    ref = ref_ops()
+    x = _activations(rows, cols, torch.float16, rows * cols).to(dev())
+    meta_ref = ref.asym_find_meta(x, bits)
+    q_ref = ref.asym_quantize_old(x, meta_ref, bits)
+    torch.cuda.synchronize()
+    meta = quik.asymmetric.find_meta(x, bits)
+    assert torch.equal(meta, meta_ref)
+    assert torch.equal(quik.asymmetric.quantizeOld(x, meta_ref, bits), q_ref)
+    assert_device_clean()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("rows,cols", [(37, 1000), (128, 4096), (2048, 264)])
+def test_asym_dequantize_equals_reference_kernel(dtype, bits, rows, cols):
+    """quik.asymmetric.dequantize (asymmetric.cu:119-233).  The reference source writes two roundings per product-sum
+    (a * b, then + c); whether the compiler fuses them is its choice, so single results may differ in the last
+    place of the fp32 intermediate: identical bytes are demanded except for at most 1e-3 of the elements, which may
+    differ by one unit in the last place of the output type."""
+    import quik
+    ref = ref_ops()
+    g = torch.Generator().manual_seed(rows * cols + bits)
+    x = torch.randint(-200000, 200000, (rows, cols), generator=g, dtype=torch.int32).to(dev())
+    meta = torch.stack([torch.rand(rows, generator=g) * 0.1 + 1e-3, torch.randn(rows, generator=g)], 1).reshape(-1).to(dtype).to(dev())
+    sc = (torch.rand(cols, 1, generator=g) * 0.01 + 1e-4).to(dtype).to(dev())
+    wr = torch.randn(1, cols, generator=g).to(dtype).to(dev())
+    y = torch.randn(rows, cols, generator=g).to(dtype).to(dev())
+    out_ref = ref.asym_dequantize(x, meta, sc, wr, y, bits)
+    torch.cuda.synchronize()
+    out = quik.asymmetric.dequantize(x, meta, sc, wr, y, bits)
+    differ = out != out_ref
+    assert differ.float().mean().item() <= 1e-3
+    if differ.any():
+        a, b = out[differ].float(), out_ref[differ].float()
+        ulp = b.abs() * (2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7)
+        assert ((a - b).abs() <= ulp + 1e-7).all()
+    assert_device_clean()
+
+
+def test_symmetric_ops_equal_reference_kernels():
+    import quik
+    ref = ref_ops()
+    torch.manual_seed(1)
+    n, k, m = 512, 2048, 256
+    src = torch.randn(n, k, dtype=torch.float16).to(dev())
+    scale = (torch.rand(n, 1) * 0.05 + 0.01).half().to(dev())
+    assert torch.equal(quik.symmetric.quantize(src, scale, 8), ref.sym_quantize_int8(src, scale))
+    small = (torch.randn(n, k) * 2).half().to(dev())
+    one = torch.ones(n, 1, dtype=torch.float16, device=dev())
+    assert torch.equal(quik.symmetric.quantize(small, one, 4), ref.sym_quantize_int4(small, one))
+    sr = torch.randn(m, 1, dtype=torch.float16).to(dev())
+    sc = torch.randn(1, n, dtype=torch.float16).to(dev())
+    y = torch.randn(m, n, dtype=torch.float16).to(dev())
+    c = torch.randn(m, n, dtype=torch.float16).to(dev())
+    assert torch.equal(quik.symmetric.dequantize(c, sr, sc, y, 16), ref.sym_dequantize_half(c, sr, sc, y))
+    ci = torch.randint(-2000, 2000, (m, n), dtype=torch.int32, device=dev())
+    assert torch.equal(quik.symmetric.dequantize(ci, sr, sc, y, 32), ref.sym_dequantize_int32(ci, sr, sc, y))
+    c8 = torch.randint(-128, 128, (m, n), dtype=torch.int8, device=dev())
+    assert torch.equal(quik.symmetric.dequantize(c8, sr, sc, y, 8), ref.sym_dequantize_int8(c8, sr, sc, y))
+    assert_device_clean()
