@@ -14,7 +14,7 @@ import pytest
 import torch
 
 from oracle import build_ref
-from tests.gpu_util import assert_device_clean, dev
+from tests.gpu_util import assert_device_clean, dev, rel_rms_err
 
 pytestmark = pytest.mark.gpu
 
@@ -103,9 +103,10 @@ def test_find_meta_and_quantize_old_equal_reference_kernels(bits, rows, cols):
 @pytest.mark.parametrize("rows,cols", [(37, 1000), (128, 4096), (2048, 264)])
 def test_asym_dequantize_equals_reference_kernel(dtype, bits, rows, cols):
     """quik.asymmetric.dequantize (asymmetric.cu:119-233).  The reference source writes two roundings per product-sum
-    (a * b, then + c); whether the compiler fuses them is its choice, so single results may differ in the last
-    place of the fp32 intermediate: identical bytes are demanded except for at most 1e-3 of the elements, which may
-    differ by one unit in the last place of the output type."""
+    (a * b, then + c); whether the compiler fuses them is its choice, so the fp32 intermediate may differ by a few of
+    its last places relative to the largest term.  Identical bytes are demanded except for at most 1e-3 of the
+    elements, which may differ by one unit in the last place of the output type plus that fp32 slack (it shows where
+    the terms cancel)."""
     import quik
     ref = ref_ops()
     g = torch.Generator().manual_seed(rows * cols + bits)
@@ -118,11 +119,13 @@ def test_asym_dequantize_equals_reference_kernel(dtype, bits, rows, cols):
     torch.cuda.synchronize()
     out = quik.asymmetric.dequantize(x, meta, sc, wr, y, bits)
     differ = out != out_ref
-    assert differ.float().mean().item() <= 1e-3
-    if differ.any():
-        a, b = out[differ].float(), out_ref[differ].float()
-        ulp = b.abs() * (2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7)
-        assert ((a - b).abs() <= ulp + 1e-7).all()
+    frac = differ.float().mean().item()
+    srow, zrow = meta[0::2].float().unsqueeze(1), meta[1::2].float().unsqueeze(1)
+    shift = 8.0 if bits == 4 else 128.0
+    terms = (x.float() * srow * sc.float().t()).abs() + ((zrow + shift * srow) * wr.float()).abs() + y.float().abs()
+    slack = out_ref.float().abs() * (2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7) + terms * 2.0 ** -21 + 1e-7
+    worst = ((out.float() - out_ref.float()).abs() / slack).max().item()
+    assert frac <= 1e-3 and worst <= 1.0, (frac, worst)
     assert_device_clean()
 
 
@@ -134,7 +137,10 @@ def test_symmetric_ops_equal_reference_kernels():
     src = torch.randn(n, k, dtype=torch.float16).to(dev())
     scale = (torch.rand(n, 1) * 0.05 + 0.01).half().to(dev())
     assert torch.equal(quik.symmetric.quantize(src, scale, 8), ref.sym_quantize_int8(src, scale))
-    small = (torch.randn(n, k) * 2).half().to(dev())
+    # The reference's 4-bit symmetric quantizer does not clamp: it hands round(x / scale) to CUTLASS's int4 type,
+    # whose constructor (in the CUTLASS version of this image) asserts on the device that the value fits.  Only
+    # values that round into [-8, 7] are fed to it.
+    small = (torch.randn(n, k) * 2).clamp(-7.4, 7.4).half().to(dev())
     one = torch.ones(n, 1, dtype=torch.float16, device=dev())
     assert torch.equal(quik.symmetric.quantize(small, one, 4), ref.sym_quantize_int4(small, one))
     sr = torch.randn(m, 1, dtype=torch.float16).to(dev())
@@ -146,4 +152,38 @@ def test_symmetric_ops_equal_reference_kernels():
     assert torch.equal(quik.symmetric.dequantize(ci, sr, sc, y, 32), ref.sym_dequantize_int32(ci, sr, sc, y))
     c8 = torch.randint(-128, 128, (m, n), dtype=torch.int8, device=dev())
     assert torch.equal(quik.symmetric.dequantize(c8, sr, sc, y, 8), ref.sym_dequantize_int8(c8, sr, sc, y))
+    assert_device_clean()
+
+
+def _unpack_nibbles(p):
+    """uint8 [R, C] of packed int4 (element 2j in the low nibble) -> int8 [R, 2C]."""
+    lo = ((p & 0xF).to(torch.int8) ^ 8) - 8
+    hi = ((p >> 4).to(torch.int8) ^ 8) - 8
+    return torch.stack([lo, hi], dim=2).reshape(p.shape[0], -1)
+
+
+@pytest.mark.parametrize("M,K,N,F,bits", [(16, 4352, 1024, 256, 4), (300, 4352, 1000, 256, 4), (2048, 4352, 2048, 256, 4),
+                                          (64, 11264, 512, 256, 8), (2048, 11264, 1024, 256, 8)])
+def test_layer_forward_vs_composition_of_reference_kernels(M, K, N, F, bits):
+    """MixedQLinear.forward of the reference (experiments/qlinear.py:105-148) rebuilt from the reference's own
+    kernels: its quantizer, an exact integer product in place of its CUTLASS GEMM (same integers by definition),
+    torch's F.linear on the outlier columns as in the reference, its dequantize kernel.  The fused layer of this
+    repository stays within the stated 1e-2 x RMS of it; the unfused operator sequence within a last place."""
+    from quik_b200.workloads import make_layer
+    ref = ref_ops()
+    case = make_layer("t", M, K, N, bits, F=F, seed=M + N, device=dev(), clip=False)
+    m, x = case.module, case.x
+    q, meta, fp_x = ref.asym_quantize(x, m.int_indices, m.fp_indices, bits)
+    qi = _unpack_nibbles(q) if bits == 4 else q
+    wi = _unpack_nibbles(m.int_weight) if bits == 4 else m.int_weight
+    acc = (qi.double() @ wi.double().t()).to(torch.int32)            # exact: |sum| < 2^53
+    fp_result = torch.nn.functional.linear(fp_x, m.fp_weight, m.bias)
+    out_ref = ref.asym_dequantize(acc, meta, m.weights_scales, m.reduced_w, fp_result, bits)
+    torch.cuda.synchronize()
+    fused = m(x.unsqueeze(0))[0]
+    assert rel_rms_err(fused, out_ref) < 1e-2
+    m.fused = False
+    unfused = m(x.unsqueeze(0))[0]
+    m.fused = True
+    assert rel_rms_err(unfused, out_ref) < 2e-3
     assert_device_clean()
