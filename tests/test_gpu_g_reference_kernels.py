@@ -187,3 +187,82 @@ def test_layer_forward_vs_composition_of_reference_kernels(M, K, N, F, bits):
     m.fused = True
     assert rel_rms_err(unfused, out_ref) < 2e-3
     assert_device_clean()
+
+
+def test_timing_against_reference_kernels(capsys):
+    """Not a parity check: times the reference's quantize and dequantize kernels next to this repository's on the
+    7B layer inputs (2048 tokens) and prints the figures (run with -s).  CUDA events around 20 replays of a graph of 8
+    launches over rotating inputs larger than L2."""
+    import quik
+    from quik_b200.qlinear import _to_u16
+    ref = ref_ops()
+    lines = []
+    for cols, nfp, bits in ((4352, 256, 4), (11264, 256, 8)):
+        xs = [_activations(2048, cols, torch.float16, i).to(dev()) for i in range(8)]
+        ints, fp = _indices(cols, nfp, "ascending", 1)
+        ints, fp = ints.to(dev()), fp.to(dev())
+        i16, f16 = _to_u16(ints), _to_u16(fp)
+
+        def timed(fn, graph):
+            # The reference's kernels launch on the legacy default stream whatever the current stream is, so they
+            # cannot be captured: they are timed eagerly (their kernels are much longer than a launch).  This
+            # repository's are also replayed from a CUDA graph, which takes the host's launch cost out.
+            for x in xs:
+                fn(x)
+            torch.cuda.synchronize()
+            if not graph:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(20):
+                    for x in xs:
+                        fn(x)
+                b.record()
+                torch.cuda.synchronize()
+                return a.elapsed_time(b) * 1e3 / 160
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for x in xs:
+                    fn(x)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for x in xs:
+                        fn(x)
+                g.replay()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(20):
+                    g.replay()
+                b.record()
+                torch.cuda.synchronize()
+            return a.elapsed_time(b) * 1e3 / 160
+
+        t_ref = timed(lambda x: ref.asym_quantize(x, ints, fp, bits), False)
+        t_eager = timed(lambda x: quik.asymmetric.quantize_u16(x, i16, f16, bits, True), False)
+        t_graph = timed(lambda x: quik.asymmetric.quantize_u16(x, i16, f16, bits, True), True)
+        lines.append(f"quantize [2048, {cols}] {bits}-bit: reference kernel {t_ref:.1f} us (eager), this repository "
+                     f"{t_eager:.1f} us (eager, host bound) / {t_graph:.1f} us (graph replay)")
+    n = 4096
+    acc = torch.randint(-200000, 200000, (2048, n), dtype=torch.int32, device=dev())
+    meta = (torch.rand(4096, device=dev()) * 0.1 + 1e-3).half()
+    sc = (torch.rand(n, 1, device=dev()) * 0.01 + 1e-4).half()
+    wr = torch.randn(1, n, device=dev()).half()
+    y = torch.randn(2048, n, device=dev()).half()
+    for name, fn in (("reference kernel", lambda: ref.asym_dequantize(acc, meta, sc, wr, y, 4)),
+                     ("this repository (discrete op; the layer fuses it into the GEMM)", lambda: quik.asymmetric.dequantize(acc, meta, sc, wr, y, 4))):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(50):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        lines.append(f"dequantize [2048, {n}]: {name} {a.elapsed_time(b) * 1e3 / 50:.1f} us")
+    with capsys.disabled():
+        print()
+        for line in lines:
+            print("  " + line)
+    assert_device_clean()
