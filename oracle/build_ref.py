@@ -1,11 +1,11 @@
-"""Build oracle/_ref/quik_ref_ops*.so: the QUIK reference's own quantize / dequantize CUDA kernels.
+"""Build oracle/_ref/quik_ref_ops*.so: the QUIK reference's own CUDA kernels.
 
 Test infrastructure, not product code.  The reference's sources are compiled where they lie (the checkout given by
-QUIK_REFERENCE_DIR, default /root/reference): src/asymmetric/asymmetric.cu and src/symmetric/symmetric.cu with the
-small binding oracle/ref_binding.cpp.  They include one header-only CUTLASS file (cutlass/subbyte_reference.h, for the
-packed-int4 reference type), taken from a CUTLASS header tree installed in the Python environment; the reference's GEMM
-and fused-dequantize sources need CUTLASS GEMM templates from a submodule that the checkout does not vendor and are
-left out.  Nothing of the reference is copied into this repository; the output directory is git-ignored.
+QUIK_REFERENCE_DIR, default /root/reference): src/asymmetric/{asymmetric,fused_dequantize}.cu,
+src/symmetric/{symmetric,fused_dequantize}.cu and src/matmul/matmul.cu with the small binding oracle/ref_binding.cpp,
+by nvcc directly (not by the reference's cmake build).  They need CUTLASS headers (the reference's own submodule is not
+vendored in the checkout); a CUTLASS header tree installed in the Python environment is used instead.  The cuSPARSELt
+path is not enabled.  Nothing of the reference is copied into this repository; the output directory is git-ignored.
 
 Usage: python oracle/build_ref.py     (prints the path of the library, or why it was not built, and exits 0)
 """
@@ -21,14 +21,17 @@ NAME = "quik_ref_ops"
 
 
 def _cutlass_include():
-    for mod, rel in (("flashinfer", "data/cutlass/include"), ("tilelang", "3rdparty/cutlass/include")):
+    """[include dir, tools/util/include dir] of a CUTLASS tree that has both, or None."""
+    for mod, rel in (("flashinfer", "data/cutlass"), ("tilelang", "3rdparty/cutlass")):
         try:
             m = __import__(mod)
         except Exception:
             continue
-        path = os.path.join(os.path.dirname(m.__file__), rel)
-        if os.path.isfile(os.path.join(path, "cutlass", "subbyte_reference.h")):
-            return path
+        root = os.path.join(os.path.dirname(m.__file__), rel)
+        inc, util = os.path.join(root, "include"), os.path.join(root, "tools", "util", "include")
+        if os.path.isfile(os.path.join(inc, "cutlass", "gemm", "device", "gemm.h")) and \
+                os.path.isfile(os.path.join(util, "cutlass", "util", "host_reorder.h")):
+            return [inc, util]
     return None
 
 
@@ -38,12 +41,14 @@ def lib_path():
 
 def build(verbose=False):
     ref = os.environ.get("QUIK_REFERENCE_DIR", "/root/reference")
-    srcs = [os.path.join(ref, "src", "asymmetric", "asymmetric.cu"), os.path.join(ref, "src", "symmetric", "symmetric.cu")]
+    srcs = [os.path.join(ref, "src", *p) for p in (("asymmetric", "asymmetric.cu"), ("asymmetric", "fused_dequantize.cu"),
+                                                   ("symmetric", "symmetric.cu"), ("symmetric", "fused_dequantize.cu"),
+                                                   ("matmul", "matmul.cu"))]
     if not all(os.path.isfile(s) for s in srcs):
         return None, f"reference sources not found under {ref}"
     cutlass = _cutlass_include()
     if cutlass is None:
-        return None, "no CUTLASS header tree with cutlass/subbyte_reference.h in this environment"
+        return None, "no CUTLASS header tree (include + tools/util/include) in this environment"
     import torch
     from torch.utils import cpp_extension as ce
 
@@ -54,13 +59,13 @@ def build(verbose=False):
         return out, "up to date"
     os.makedirs(OUT_DIR, exist_ok=True)
     nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
-    inc = [os.path.join(ref, "include"), cutlass, sysconfig.get_paths()["include"]] + ce.include_paths("cuda")
+    inc = [os.path.join(ref, "include"), *cutlass, sysconfig.get_paths()["include"]] + ce.include_paths("cuda")
     # the half-operator switches are the ones the reference's own CMakeLists.txt (lines 77-80) passes to nvcc
     common = ["-O2", "-std=c++17", "-DCUDA_HAS_FP16=1", "-D__CUDA_NO_HALF_OPERATORS__", "-D__CUDA_NO_HALF_CONVERSIONS__",
               "-D__CUDA_NO_HALF2_OPERATORS__", "-D__CUDA_NO_BFLOAT16_CONVERSIONS__",
               "-DTORCH_EXTENSION_NAME=" + NAME, "-DTORCH_API_INCLUDE_EXTENSION_H",
               "-D_GLIBCXX_USE_CXX11_ABI=" + str(int(torch._C._GLIBCXX_USE_CXX11_ABI))] + ["-I" + i for i in inc]
-    # the three translation units take minutes each (torch headers under nvcc): compile them side by side
+    # the translation units take minutes each (torch and CUTLASS headers under nvcc): compile them side by side
     objs, procs = [], []
     for i, src in enumerate(srcs + [binding]):
         obj = os.path.join(OUT_DIR, f"ref_{i}.o")

@@ -189,6 +189,99 @@ def test_layer_forward_vs_composition_of_reference_kernels(M, K, N, F, bits):
     assert_device_clean()
 
 
+def _pack_i4(v):
+    """int8 [R, C] of codes in [-8, 7] -> uint8 [R, C/2], element 2j in the low nibble."""
+    u = (v.to(torch.int16) & 0xF).to(torch.uint8)
+    return (u[:, 0::2] | (u[:, 1::2] << 4)).contiguous()
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 1024), (300, 520, 2048), (2048, 4096, 4096), (1, 128, 11008), (2048, 1024, 11008)])
+def test_int_matmul_equals_reference_cutlass_gemm(bits, M, N, K):
+    """quik.matmul.int4Matmul / int8Matmul against the reference's CUTLASS GEMMs (matmul.cu:17-55,98-136): the same
+    int32 values, bit for bit."""
+    import quik
+    ref = ref_ops()
+    g = torch.Generator().manual_seed(M + N + K + bits)
+    lo, hi = (-8, 8) if bits == 4 else (-128, 128)
+    a = torch.randint(lo, hi, (M, K), generator=g, dtype=torch.int8).to(dev())
+    b = torch.randint(lo, hi, (N, K), generator=g, dtype=torch.int8).to(dev())
+    if bits == 4:
+        a, b = _pack_i4(a), _pack_i4(b)
+        c_ref = ref.int4_matmul(a, b)
+        torch.cuda.synchronize()
+        c = quik.matmul.int4Matmul(a, b)
+    else:
+        c_ref = ref.int8_matmul(a, b)
+        torch.cuda.synchronize()
+        c = quik.matmul.int8Matmul(a, b)
+    assert c.dtype == c_ref.dtype and torch.equal(c, c_ref)
+    assert_device_clean()
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_fused_dequantize_ops_vs_reference_fused_kernels(bits):
+    """The reference's fused GEMM + dequantize ops (asymmetric and symmetric fused_dequantize.cu) on the data of its
+    own test (test/python/test_fused.py:40-67).  The reference evaluates the epilogue in fp16, this repository in
+    fp32 with one rounding: agreement within three fp16 units of the largest term."""
+    import quik
+    ref = ref_ops()
+    M, N, K = 1024, 5120, 2048
+    g = torch.Generator().manual_seed(2)
+    a_i = torch.randint(-3, 3, (M, K), generator=g, dtype=torch.int8).to(dev())
+    b_i = torch.randint(-3, 3, (N, K), generator=g, dtype=torch.int8).to(dev())
+    a, b = (_pack_i4(a_i), _pack_i4(b_i)) if bits == 4 else (a_i, b_i)
+    sr = torch.rand(M, 1, generator=g).half().to(dev())
+    sc = torch.rand(1, N, generator=g).half().to(dev())
+    zr = torch.rand(M, 1, generator=g).half().to(dev())
+    wr = torch.rand(1, N, generator=g).half().to(dev())
+    y = torch.rand(M, N, generator=g).half().to(dev())
+    sv = 0.4376
+    if bits == 4:
+        out_ref = ref.asym_int4_fused_dequantize(a, b, sr, sc, sv, zr, wr, y)
+        outs_ref = ref.sym_int4_fused_dequantize(a, b, sr, sc, y)
+        torch.cuda.synchronize()
+        out = quik.asymmetric.int4FusedDequantize(a, b, sr, sc, sv, zr, wr, y)
+        outs = quik.symmetric.int4FusedDequantize(a, b, sr, sc, y)
+    else:
+        out_ref = ref.asym_int8_fused_dequantize(a, b, sr, sc, sv, zr, wr, y)
+        outs_ref = ref.sym_int8_fused_dequantize(a, b, sr, sc, y)
+        torch.cuda.synchronize()
+        out = quik.asymmetric.int8FusedDequantize(a, b, sr, sc, sv, zr, wr, y)
+        outs = quik.symmetric.int8FusedDequantize(a, b, sr, sc, y)
+    acc = (a_i.double() @ b_i.double().t()).float()
+    t1 = (acc * sr.float() * sc.float()).abs()
+    t2 = ((zr.float() + sv * sr.float()) * wr.float()).abs()
+    ulp = torch.maximum(torch.maximum(t1, t2), torch.maximum(y.float().abs(), out_ref.float().abs())) * 2 ** -10
+    assert ((out.float() - out_ref.float()).abs() <= 3 * ulp).all()
+    ulp_s = torch.maximum(torch.maximum(t1, y.float().abs()), outs_ref.float().abs()) * 2 ** -10
+    assert ((outs.float() - outs_ref.float()).abs() <= 3 * ulp_s).all()
+    assert_device_clean()
+
+
+def _reference_forward(ref, m, x, bits):
+    """MixedQLinear.forward of the reference (experiments/qlinear.py:105-148), op for op, on the reference's kernels."""
+    q, meta, fp_x = ref.asym_quantize(x, m.int_indices, m.fp_indices, bits)
+    fp_result = torch.nn.functional.linear(fp_x, m.fp_weight, m.bias)
+    acc = ref.int4_matmul(q, m.int_weight) if bits == 4 else ref.int8_matmul(q, m.int_weight)
+    return ref.asym_dequantize(acc, meta, m.weights_scales, m.reduced_w, fp_result, bits)
+
+
+@pytest.mark.parametrize("M,K,N,F,bits", [(16, 4352, 1024, 256, 4), (128, 4352, 4096, 256, 4), (2048, 4352, 4096, 256, 4),
+                                          (64, 11264, 512, 256, 8), (2048, 11264, 4096, 256, 8)])
+def test_layer_forward_vs_reference_forward(M, K, N, F, bits):
+    """The whole reference layer on the reference's own kernels (quantize, CUTLASS GEMM, F.linear, dequantize)
+    against this repository's fused layer: max-abs difference below 1e-2 of the output RMS."""
+    from quik_b200.workloads import make_layer
+    ref = ref_ops()
+    case = make_layer("t", M, K, N, bits, F=F, seed=M + N, device=dev(), clip=False)
+    out_ref = _reference_forward(ref, case.module, case.x, bits)
+    torch.cuda.synchronize()
+    out = case.module(case.x.unsqueeze(0))[0]
+    assert rel_rms_err(out, out_ref) < 1e-2
+    assert_device_clean()
+
+
 def test_timing_against_reference_kernels(capsys):
     """Not a parity check: times the reference's quantize and dequantize kernels next to this repository's on the
     7B layer inputs (2048 tokens) and prints the figures (run with -s).  CUDA events around 20 replays of a graph of 8
@@ -261,6 +354,52 @@ def test_timing_against_reference_kernels(capsys):
         b.record()
         torch.cuda.synchronize()
         lines.append(f"dequantize [2048, {n}]: {name} {a.elapsed_time(b) * 1e3 / 50:.1f} us")
+    # whole layers: the reference's operator sequence on its own kernels (eager; they cannot be captured) against this
+    # repository's fused layer (eager and replayed from a graph)
+    from quik_b200.workloads import make_layer
+    for name, K, N, bits in (("qkv", 4352, 12288, 4), ("o", 4352, 4096, 4), ("gate+up", 4352, 22016, 4), ("down", 11264, 4096, 8)):
+        case = make_layer(name, 2048, K, N, bits, F=256, seed=0, device=dev(), clip=False)
+        m, x = case.module, case.x
+
+        def run_ref():
+            return _reference_forward(ref, m, x, bits)
+
+        def run_ours():
+            return m(x.unsqueeze(0))
+
+        times = []
+        for fn in (run_ref, run_ours):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(10):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3 / 10)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            run_ours()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                run_ours()
+            g.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(10):
+                g.replay()
+            b.record()
+            torch.cuda.synchronize()
+        ops = 2.0 * 2048 * N * K
+        lines.append(f"layer {name} [2048 x {K}] -> {N}, {bits}-bit: reference kernels {times[0]:.0f} us ({ops / times[0] / 1e6:.0f} TOPS), "
+                     f"this repository {times[1]:.0f} us eager / {a.elapsed_time(b) * 100:.0f} us graph "
+                     f"({ops / (a.elapsed_time(b) * 100) / 1e6:.0f} TOPS)")
+        del case, m, x
+        torch.cuda.empty_cache()
     with capsys.disabled():
         print()
         for line in lines:
