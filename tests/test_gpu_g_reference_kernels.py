@@ -282,6 +282,37 @@ def test_layer_forward_vs_reference_forward(M, K, N, F, bits):
     assert_device_clean()
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bits", [4, 8])
+def test_cpu_oracle_matches_reference_kernels(dtype, bits):
+    """The CPU oracle itself (oracle/kernel_path.py) against the reference's kernels: quantizer codes exact except at
+    most 1e-5 of the codes off by one (the device's reciprocal-based half division against an IEEE division), meta and
+    outlier columns exact, dequantize exact up to the same fused-multiply-add freedom as the kernels, layer forward
+    within 1e-2 x RMS."""
+    from oracle import kernel_path as kp
+    from quik_b200.workloads import make_layer
+    ref = ref_ops()
+    rows, cols, nfp = 64, 4352, 256
+    x = _activations(rows, cols, dtype, 11 + bits)
+    ints, fp = _indices(cols, nfp, "ascending", 3)
+    q_ref, meta_ref, fp_ref = ref.asym_quantize(x.to(dev()), ints.to(dev()), fp.to(dev()), bits)
+    q, meta, fp_x = kp.asym_quantize(x, ints, fp, bits)
+    assert torch.equal(meta, meta_ref.cpu()) and torch.equal(fp_x, fp_ref.cpu())
+    codes = _unpack_nibbles(q) if bits == 4 else q
+    codes_ref = _unpack_nibbles(q_ref.cpu()) if bits == 4 else q_ref.cpu()
+    diff = (codes.to(torch.int16) - codes_ref.to(torch.int16)).abs()
+    assert diff.max() <= 1 and (diff != 0).float().mean() <= 1e-5
+    if dtype == torch.float16:
+        case = make_layer("t", 64, 4352, 512, bits, F=256, seed=5, device=dev(), clip=False)
+        m = case.module
+        buf = {"int_weight": m.int_weight.cpu(), "weights_scales": m.weights_scales.cpu(), "reduced_w": m.reduced_w.cpu(),
+               "int_indices": m.int_indices.cpu(), "fp_indices": m.fp_indices.cpu(), "fp_weight": m.fp_weight.cpu(), "bias": None}
+        out_oracle = kp.mixed_linear_forward(case.x.cpu(), buf, bits, round_y=True)
+        out_ref = _reference_forward(ref, m, case.x, bits)
+        assert rel_rms_err(out_oracle, out_ref.cpu()) < 1e-2
+    assert_device_clean()
+
+
 def test_timing_against_reference_kernels(capsys):
     """Not a parity check: times the reference's quantize and dequantize kernels next to this repository's on the
     7B layer inputs (2048 tokens) and prints the figures (run with -s).  CUDA events around 20 replays of a graph of 8
