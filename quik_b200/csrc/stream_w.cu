@@ -41,21 +41,21 @@ constexpr int SW_A_COLS = 64;                      // 256 int8 codes per row = 6
 constexpr int SW_ACCS = 2;                         // one s32 accumulator per issuing thread, summed at the end
 constexpr int SW_AUX_BYTES = 2048;
 
-// Sizes that depend on NTOK, the MMA's N: the number of tokens (16, 64 or 128; tokens beyond M read as zero).  A
+// Sizes that depend on NTOK, the MMA's N: the number of tokens (16, 32, 64 or 128; tokens beyond M read as zero).  A
 // tcgen05.mma costs the same for every N up to 64, so up to 64 tokens ride along with the weight stream for free.
 template <int NTOK> struct SwCfg {
   static constexpr int X_BYTES = NTOK * 128;                        // one 128-byte k-block of the token operand
   static constexpr int STAGE_BYTES = SW_W_BYTES + 2 * X_BYTES;      // int4: 256 codes of W need two token blocks
-  static constexpr int CTAS_PER_SM = NTOK == 16 ? 2 : 1;
-  static constexpr int STAGES = NTOK == 128 ? 3 : 5;
-  static constexpr int A_SLOTS = NTOK == 128 ? 2 : 3;               // TMEM ring of widened W k-blocks
+  static constexpr int CTAS_PER_SM = NTOK <= 32 ? 2 : 1;
+  static constexpr int STAGES = (NTOK == 128 || NTOK == 32) ? 3 : 5;
+  static constexpr int A_SLOTS = (NTOK == 128 || NTOK == 32) ? 2 : 3;   // TMEM ring of widened W k-blocks
   static constexpr int D_INT = A_SLOTS * SW_A_COLS;                 // TMEM column of the first s32 accumulator
   static constexpr int D_FP = D_INT + SW_ACCS * NTOK;               // ... of the f32 accumulator
-  static constexpr int TMEM_COLS = NTOK == 16 ? 256 : 512;          // NTOK 16: two CTAs per SM share the 512 columns
+  static constexpr int TMEM_COLS = NTOK <= 32 ? 256 : 512;          // NTOK 16, 32: two CTAs per SM share the 512 columns
   static constexpr int RED_BYTES = NTOK * SW_ROWS * 4;
   static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + RED_BYTES + SW_AUX_BYTES;
   static_assert(D_FP + NTOK <= TMEM_COLS, "TMEM plan");
-  static_assert(SMEM <= 227 * 1024, "shared-memory plan");
+  static_assert(SMEM <= (227 * 1024) / CTAS_PER_SM - 1024 * (CTAS_PER_SM - 1), "shared-memory plan");
 };
 
 struct StreamParams {
@@ -478,9 +478,9 @@ int launch_stream_w(const void *q, const void *w, int bits, int M, int N, int K_
   if (has_fp && (ep.F % 8 != 0 || !aligned16(ep.fp_a) || !aligned16(ep.fp_b))) return QUIK_ERR_ALIGN;
   if (ep.meta == nullptr || ep.w_reduced == nullptr || ep.y != nullptr) return QUIK_ERR_UNSUPPORTED;
 
-  const int ntok = M <= 16 ? 16 : (M <= 64 ? 64 : 128);          // the MMA's N
-  const int ctas_per_sm = ntok == 16 ? 2 : 1;
-  const int stages = ntok == 128 ? 3 : 5;
+  const int ntok = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));          // the MMA's N
+  const int ctas_per_sm = ntok <= 32 ? 2 : 1;
+  const int stages = (ntok == 128 || ntok == 32) ? 3 : 5;
   StreamParams p{};
   p.M = M;
   p.N = N;
@@ -523,6 +523,7 @@ int launch_stream_w(const void *q, const void *w, int bits, int M, int N, int K_
 #define QUIK_SW(T, B)                                                                    \
   do {                                                                                   \
     if (ntok == 16) return launch_t<T, B, 16>(tw, tx, tfw, tfx, p, slabs, st);           \
+    if (ntok == 32) return launch_t<T, B, 32>(tw, tx, tfw, tfx, p, slabs, st);           \
     if (ntok == 64) return launch_t<T, B, 64>(tw, tx, tfw, tfx, p, slabs, st);           \
     return launch_t<T, B, 128>(tw, tx, tfw, tfx, p, slabs, st);                          \
   } while (0)
