@@ -5,7 +5,7 @@
 // format: packed int4 (two codes per byte, low nibble first, QUIK include/int4.h:78-98) or int8.
 //
 // The product is computed transposed, out^T[n, m] = sum_k W[n, k] * Xq[m, k]: 128 weight rows are the
-// M = 128 operand of tcgen05.mma, the tokens (zero-padded to NTOK = 16, 64 or 128) its N operand, so one
+// M = 128 operand of tcgen05.mma, the tokens (zero-padded to NTOK = 16, 32, 64 or 128) its N operand, so one
 // instruction consumes 128 x 32 weight codes.  Per CTA (one 128-row slab of W, one share of K):
 //   warp 0      TMA producer: k-blocks of W (128 rows x 128 bytes, 128B swizzle) and of the token codes /
 //               outlier values (NTOK rows x 128 bytes) into a ring of shared-memory stages.

@@ -1,10 +1,11 @@
 """GPU parity against the reference's OWN CUDA kernels on the same inputs.
 
-oracle/build_ref.py compiles the QUIK reference's quantize / quantizeOld / find_meta / dequantize and symmetric
-quantize / dequantize kernels unmodified from the reference checkout (src/asymmetric/asymmetric.cu,
-src/symmetric/symmetric.cu) into oracle/_ref/.  These tests run them next to this repository's kernels and demand
-identical bytes.  They are skipped when that library is absent (it is built where the reference checkout is
-available and travels with the repository's other built files).
+oracle/build_ref.py compiles the QUIK reference's CUDA sources unmodified from the reference checkout
+(src/asymmetric/{asymmetric,fused_dequantize}.cu, src/symmetric/{symmetric,fused_dequantize}.cu, src/matmul/matmul.cu:
+quantize, quantizeOld, find_meta, dequantize, the symmetric ops, the CUTLASS int4 / int8 GEMMs and the fused GEMM +
+dequantize ops) into oracle/_ref/.  These tests run them on the GPU next to this repository's kernels, and next to the
+CPU oracle, on the same inputs.  They are skipped when that library is absent (it is built where the reference
+checkout is available and travels with the repository's other built files).
 
 Shapes respect what the reference kernels assume: at least 1024 elements (its block size then is the power of two its
 tree reduction needs), at least 1024 columns for the fused quantizer (one row per block: its blocks do not
