@@ -46,7 +46,8 @@ extern "C" {
 #define QUIK_ENGINE_MMA_SYNC   2
 /* Output-tile width of the tcgen05 engine: 0 = chosen by shape, 128 or 256. */
 #define QUIK_CFG_TILE_N        2
-/* Layers with M <= QUIK_SMALL_M_MAX tokens: 1 (default) weight streaming, engine chosen by the size of the
+/* Layers with few tokens (8-bit layers with 17 to QUIK_STREAM_M_MAX tokens always use the tcgen05 streaming engine
+ * unless this is 0).  M <= QUIK_SMALL_M_MAX tokens: 1 (default) weight streaming, engine chosen by the size of the
  * weights; 2 mma.sync fed by direct loads; 3 tcgen05 fed by a TMA ring (8-bit layers, and 4-bit layers whose token
  * codes come one per byte); 4 mma.sync fed by a TMA ring; 0 the tensor-core GEMM for 8-bit layers.
  * (4-bit layers also choose by the operand layout, see quik_mixed_linear.) */
@@ -196,7 +197,7 @@ int quik_fused_dequantize(const void *A, const void *B, int bits,
  *   out      [M, N] dtype
  * 4-bit layers choose the engine by the operand layout:
  *   q one per byte, w one per byte   tensor-core GEMM (any M);
- *   q one per byte, w packed         weight streaming on tcgen05 (M <= QUIK_SMALL_M_MAX, K_int % 32 == 0): the
+ *   q one per byte, w packed         weight streaming on tcgen05 (M <= QUIK_STREAM_M_MAX, K_int % 32 == 0): the
  *                                    packed weights are widened on chip on their way to the tensor cores;
  *   q packed,       w packed         weight streaming on mma.sync, direct loads or TMA ring by QUIK_CFG_SMALL_M
  *                                    (M <= QUIK_SMALL_M_MAX, K_int % 32 == 0).
