@@ -14,6 +14,7 @@ import os
 import subprocess
 import sys
 import sysconfig
+import time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
@@ -74,8 +75,16 @@ def build(verbose=False):
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
         objs.append(obj)
     failed = None
+    limit = float(os.environ.get("QUIK_REF_BUILD_TIMEOUT", "1500"))      # seconds for all translation units together
+    deadline = time.monotonic() + limit
     for src, pr in procs:
-        _, err = pr.communicate()
+        try:
+            _, err = pr.communicate(timeout=max(1.0, deadline - time.monotonic()))
+        except subprocess.TimeoutExpired:
+            for _, other in procs:
+                if other.poll() is None:
+                    other.kill()
+            return None, f"compilation did not finish within {limit:.0f} s"
         if pr.returncode != 0 and failed is None:
             lines = [l for l in err.splitlines() if "error" in l]
             failed = f"nvcc failed for {os.path.basename(src)}: " + " | ".join(lines[:4])
