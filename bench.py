@@ -448,8 +448,29 @@ def main():
                 ts.append(a.elapsed_time(b))
             med = statistics.median(ts)
             block = {"workload": "one Llama-2-7B decoder block (hidden 4096, 32 heads, intermediate 11008, RMSNorm, RoPE, "
-                                 "SDPA), all 7 linears MixedQLinear (down int8), batch 1 x 2048 tokens, eager launches",
-                     "ms": med, "prefill_tokens_per_s_per_block": 2048 / (med * 1e-3)}
+                                 "SDPA), all 7 linears MixedQLinear (down int8), batch 1 x 2048 tokens",
+                     "ms": med, "prefill_tokens_per_s_per_block": 2048 / (med * 1e-3), "launch_mode": "eager"}
+            try:        # the same block replayed from a CUDA graph (takes the host's launch cost out)
+                side = torch.cuda.Stream()
+                with torch.cuda.stream(side):
+                    blk(xb)
+                    torch.cuda.synchronize()
+                    bg = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(bg, stream=side):
+                        blk(xb)
+                    bg.replay()
+                    torch.cuda.synchronize()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    for _ in range(10):
+                        bg.replay()
+                    b.record()
+                    torch.cuda.synchronize()
+                gms = a.elapsed_time(b) / 10
+                block.update({"eager_ms": med, "ms": gms, "prefill_tokens_per_s_per_block": 2048 / (gms * 1e-3),
+                              "launch_mode": "cuda graph replay"})
+            except Exception as exc:  # pragma: no cover
+                block["graph_error"] = str(exc)[:120]
         except Exception as exc:  # pragma: no cover
             block = {"error": str(exc)[:200]}
 
