@@ -97,6 +97,33 @@ class MixedQLinear(torch.nn.Module):
             self.register_buffer('reduced_w', torch.zeros((1, self.out_features), dtype=dtype))
         self._cache = {}
 
+    @classmethod
+    def concat(cls, modules):
+        """One layer whose output is the outputs of ``modules`` side by side.
+
+        For layers that read the same input through the same column split (q/k/v, gate/up: a shared-input group of
+        experiments/llama.py:402-411): per-channel scales, reduced_w, the integer and the outlier weights are simply
+        stacked along the output dimension, so every output column is computed exactly as in its own layer, in one
+        quantizer call and one fused launch instead of one launch per member."""
+        m0 = modules[0]
+        for m in modules[1:]:
+            assert (m.bits, m.symmetric, m.in_features, m.fp_features_num, m.dtype) == \
+                   (m0.bits, m0.symmetric, m0.in_features, m0.fp_features_num, m0.dtype), "layers differ in format"
+            assert torch.equal(m.int_indices, m0.int_indices) and torch.equal(m.fp_indices, m0.fp_indices), \
+                "layers differ in their outlier columns"
+            assert (m.bias is None) == (m0.bias is None)
+        out = cls(m0.in_features, sum(m.out_features for m in modules), fp_features_num=m0.fp_features_num,
+                  symm=m0.symmetric, bits=m0.bits, dtype=m0.dtype)
+        out.weights_scales = torch.cat([m.weights_scales for m in modules], 0)
+        out.int_weight = torch.cat([m.int_weight for m in modules], 0).contiguous()
+        out.bias = None if m0.bias is None else torch.cat([m.bias for m in modules], 0)
+        out.int_indices, out.fp_indices = m0.int_indices, m0.fp_indices
+        if m0.fp_features_num > 0:
+            out.fp_weight = torch.cat([m.fp_weight for m in modules], 0).contiguous()
+        if not m0.symmetric:
+            out.reduced_w = torch.cat([m.reduced_w for m in modules], 1).contiguous()
+        return out
+
     # ------------------------------------------------------------------ derived, lazily built operands
     def _cached(self, name, src: Tensor, make):
         key = (src.data_ptr(), src._version, str(src.device))

@@ -41,3 +41,26 @@ def test_block_fused_matches_unfused_and_dense(hidden, heads, inter, seq):
     rel = ((out.float() - dense.float()).pow(2).mean().sqrt() / dense.float().pow(2).mean().sqrt()).item()
     assert rel < 0.5, rel
     assert_device_clean()
+
+
+@pytest.mark.parametrize("hidden,heads,inter,seq", [(512, 8, 1408, 96), (4096, 32, 11008, 16), (4096, 32, 11008, 256)])
+def test_block_with_stacked_groups_matches_member_layers(hidden, heads, inter, seq):
+    """k/v/q and up/gate as one layer each (MixedQLinear.concat): every output column is computed as in its member
+    layer, so the block's output agrees with the member-wise block to the last place of a few elements at most."""
+    blk = QuikLlamaBlock(hidden, heads, inter, fp_features=64 if hidden < 4096 else 256, seed=0, device=dev(), clip=False)
+    x = torch.randn(1, seq, hidden, generator=torch.Generator().manual_seed(2)).half().to(dev())
+    separate = blk(x).clone()
+    # the stacked layers alone: identical columns
+    h = blk._rms_norm(x, blk.input_norm)
+    blk.fuse_groups(True)
+    stacked = blk._fused_groups[0](h)[0]
+    members = torch.cat([blk.k_proj(h)[0], blk.v_proj(h)[0], blk.q_proj(h)[0]], dim=-1)
+    d = (stacked.float() - members.float()).abs().max() / members.float().pow(2).mean().sqrt()
+    assert d.item() < 2e-3
+    together = blk(x)
+    rms = separate.float().pow(2).mean().sqrt()
+    assert ((together.float() - separate.float()).pow(2).mean().sqrt() / rms).item() < 1e-2
+    assert "_fused_groups" not in "".join(blk.state_dict().keys())
+    blk.fuse_groups(False)
+    assert torch.equal(blk(x), separate)
+    assert_device_clean()
