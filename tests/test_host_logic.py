@@ -88,3 +88,27 @@ def test_make_layer_on_cpu_is_consistent():
     assert torch.equal(half.module.reduced_w, full.module.reduced_w[:, 16:32])
     assert torch.equal(half.x, full.x)
     assert c.ops == 2.0 * 8 * 32 * 128
+
+
+def test_concat_stacks_member_layers():
+    """MixedQLinear.concat: buffers of layers with the same column split stacked along the output dimension."""
+    torch.manual_seed(0)
+    K, F = 256, 32
+    fp_idx = torch.randperm(K)[:F].sort()[0]
+    mods = []
+    for n in (64, 32, 96):
+        lin = torch.nn.Linear(K, n, bias=False)
+        w = (0.02 * torch.randn(n, K)).half()
+        scales = w.float().abs().max(1, keepdim=True)[0] / 7
+        mods.append(qlinear.MixedQLinear.from_float(lin, w, scales, fp_indices=fp_idx, bits=4))
+    cat = qlinear.MixedQLinear.concat(mods)
+    assert cat.out_features == 192 and cat.in_features == K and cat.fp_features_num == F
+    assert torch.equal(cat.int_weight, torch.cat([m.int_weight for m in mods], 0))
+    assert torch.equal(cat.weights_scales, torch.cat([m.weights_scales for m in mods], 0))
+    assert torch.equal(cat.reduced_w, torch.cat([m.reduced_w for m in mods], 1))
+    assert torch.equal(cat.fp_weight, torch.cat([m.fp_weight for m in mods], 0))
+    assert torch.equal(cat.int_indices, mods[0].int_indices) and torch.equal(cat.fp_indices, mods[0].fp_indices)
+    other = qlinear.MixedQLinear.from_float(torch.nn.Linear(K, 8, bias=False), (0.02 * torch.randn(8, K)).half(),
+                                            torch.ones(8, 1), fp_indices=torch.arange(F), bits=4)
+    with pytest.raises(AssertionError):
+        qlinear.MixedQLinear.concat([mods[0], other])
