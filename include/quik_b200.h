@@ -44,7 +44,8 @@ extern "C" {
 #define QUIK_ENGINE_AUTO       0    /* tcgen05 + TMA + TMEM where the shape allows, else mma.sync */
 #define QUIK_ENGINE_TCGEN05    1
 #define QUIK_ENGINE_MMA_SYNC   2
-/* Output-tile width of the tcgen05 engine: 0 = chosen by shape, 128 or 256. */
+/* Output-tile width of the tcgen05 engine: 0 = chosen per problem (so that the tiles fill whole waves of CTAs),
+ * else a multiple of 16 from 32 to 256. */
 #define QUIK_CFG_TILE_N        2
 /* Layers with few tokens (8-bit layers with 17 to QUIK_STREAM_M_MAX tokens always use the tcgen05 streaming engine
  * unless this is 0).  M <= QUIK_SMALL_M_MAX tokens: 1 (default) weight streaming, engine chosen by the size of the
@@ -64,8 +65,14 @@ const char *quik_version(void);
 const char *quik_strerror(int status);
 /* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
 const char *quik_last_cuda_error(void);
+/* The settings are process-wide single words meant to be set before the layers run.  Setting one while other threads
+ * launch is safe but each of those launches sees either the old or the new value. */
 int quik_config_set(int key, int value);
 int quik_config_get(int key);
+/* Diagnostics: the tile shape the tcgen05 engine would use on the current device for M tokens, N output channels,
+ * K_int integer and F outlier columns: CTAs per tile (1, or 2 = a CTA pair working on 256 rows) and tile width.
+ * No reference counterpart (CUTLASS fixes one threadblock shape per kernel, src/matmul/matmul.cu:24-34). */
+int quik_gemm_plan(int M, int N, int K_int, int F, int *ctas, int *block_n);
 /* Every on-device wait (mbarrier, flag) is bounded; a kernel whose wait ran out records it in a
  * per-device status word and returns early.  This call synchronises the current device, returns
  * QUIK_OK or QUIK_ERR_DEVICE_WAIT, and clears the word when `clear` is non-zero. */

@@ -30,6 +30,7 @@ SIGNATURES = {
     "quik_config_set": (_i, [_i, _i]),
     "quik_config_get": (_i, [_i]),
     "quik_device_status": (_i, [_i]),
+    "quik_gemm_plan": (_i, [_i, _i, _i, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "quik_debug_counters": (_i, [_vp]),
     "quik_asym_quantize": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp]),
     "quik_asym_quantize_u16": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),

@@ -3,6 +3,7 @@
 // src/asymmetric/asymmetric.cu:185-196,519-524, src/matmul/matmul.cpp:8-48) as status codes.
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -10,9 +11,11 @@
 namespace quik {
 namespace {
 thread_local char g_err[256] = "";
-int g_engine = QUIK_ENGINE_AUTO;
-int g_small_m = 1;
-int g_pdl = 1;
+// Process-wide settings of quik_config_set: single words, read once per launch.  They are meant to be set before the
+// layers run; changing one while other threads launch gives each launch the old or the new value, never a mix.
+std::atomic<int> g_engine{QUIK_ENGINE_AUTO};
+std::atomic<int> g_small_m{1};
+std::atomic<int> g_pdl{1};
 }  // namespace
 
 void set_cuda_error(cudaError_t e, const char *where) {
@@ -22,15 +25,15 @@ void set_cuda_error(cudaError_t e, const char *where) {
 bool pdl_enabled() { return g_pdl != 0; }
 
 int num_sms() {
-  static int cached[64];
+  static std::atomic<int> cached[kMaxDevices];
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  int n = cached[dev].load();
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
+    cached[dev].store(n);
   }
-  return cached[dev];
+  return n;
 }
 
 static bool dtype_ok(int dtype) { return dtype == QUIK_F16 || dtype == QUIK_BF16; }
@@ -75,7 +78,7 @@ int quik_config_set(int key, int value) {
     return QUIK_OK;
   }
   if (key == QUIK_CFG_TILE_N) {
-    if (value != 0 && value != 128 && value != 256) return QUIK_ERR_UNSUPPORTED;
+    if (value != 0 && (value < 32 || value > 256 || value % 16 != 0)) return QUIK_ERR_UNSUPPORTED;
     set_tile_n(value);
     return QUIK_OK;
   }
@@ -106,6 +109,12 @@ int quik_config_get(int key) {
 }
 
 int quik_device_status(int clear) { return device_status_read(clear); }
+
+int quik_gemm_plan(int M, int N, int K_int, int F, int *ctas, int *block_n) {
+  if (M <= 0 || N <= 0 || K_int <= 0 || F < 0 || !ctas || !block_n) return QUIK_ERR_SHAPE;
+  choose_tile(M, N, (K_int + 127) / 128 + (F + 63) / 64, ctas, block_n);
+  return QUIK_OK;
+}
 
 int quik_debug_counters(void *device_buffer) {
   set_debug_counters(device_buffer);
@@ -297,6 +306,7 @@ int quik_mixed_linear_ld(const void *q, int q_packed, const void *w, int w_packe
   if (!q || !w || !meta || !scale_col || !w_reduced || !out) return QUIK_ERR_NULL;
   if (F > 0 && (!fp_x || !fp_w)) return QUIK_ERR_NULL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int small_m = g_small_m.load();
   Epilogue ep{};
   ep.mode = 1;
   ep.dtype = dtype;
@@ -317,7 +327,7 @@ int quik_mixed_linear_ld(const void *q, int q_packed, const void *w, int w_packe
     if (q_packed) {
       // mma.sync engines, both operands packed.  Automatic mode: layers of >= 16 MiB of packed weights go
       // through the TMA-fed ring (it streams faster), smaller ones to the direct-load kernel (it starts faster).
-      const bool ring = g_small_m == 4 || (g_small_m == 1 && (size_t)N * (size_t)K_int / 2 >= ((size_t)16 << 20));
+      const bool ring = small_m == 4 || (small_m == 1 && (size_t)N * (size_t)K_int / 2 >= ((size_t)16 << 20));
       return ring ? launch_stream_w_mma(q, w, 4, M, N, K_int, ep, st) : launch_small_m(q, w, 4, M, N, K_int, ep, st);
     }
     return launch_stream_w(q, w, 4, M, N, K_int, ep, st);                   // tcgen05, token codes one per byte
@@ -326,9 +336,9 @@ int quik_mixed_linear_ld(const void *q, int q_packed, const void *w, int w_packe
   // weights (measured on 7B and 70B down projections): >= 128 MiB tcgen05 (0.91 of the HBM rate), >= 32 MiB mma.sync
   // behind the TMA ring (0.87 on the large layer, the fastest on the 45 MiB one), below that mma.sync with direct
   // loads (shortest start-up).
-  if (bits == 8 && M <= QUIK_SMALL_M_MAX && g_small_m != 0) {
+  if (bits == 8 && M <= QUIK_SMALL_M_MAX && small_m != 0) {
     const size_t wbytes = (size_t)N * (size_t)K_int;
-    int engine = g_small_m;
+    int engine = small_m;
     if (engine == 1) engine = wbytes >= ((size_t)128 << 20) ? 3 : (wbytes >= ((size_t)32 << 20) ? 4 : 2);
     if (engine == 3) return launch_stream_w(q, w, 8, M, N, K_int, ep, st);
     if (engine == 4) return launch_stream_w_mma(q, w, 8, M, N, K_int, ep, st);
@@ -336,7 +346,7 @@ int quik_mixed_linear_ld(const void *q, int q_packed, const void *w, int w_packe
   }
   // 17 to 128 tokens: the tcgen05 streaming engine takes them at the cost of 16 (the tensor-core GEMM would leave
   // most SMs idle at these sizes)
-  if (bits == 8 && M <= QUIK_STREAM_M_MAX && g_small_m != 0) return launch_stream_w(q, w, 8, M, N, K_int, ep, st);
+  if (bits == 8 && M <= QUIK_STREAM_M_MAX && small_m != 0) return launch_stream_w(q, w, 8, M, N, K_int, ep, st);
   return run_int8_gemm(static_cast<const int8_t *>(q), static_cast<const int8_t *>(w), M, N, K_int, ep, st);
 }
 
@@ -357,14 +367,14 @@ static __device__ __align__(256) unsigned char g_fixed_scratch[QUIK_NOALLOC_SCRA
 
 namespace {
 std::mutex g_fixed_mutex;
-void *g_fixed_ptr[64] = {};      // device address of g_fixed_scratch, looked up once per device
+void *g_fixed_ptr[kMaxDevices] = {};      // device address of g_fixed_scratch, looked up once per device
 
 // In host code `g_fixed_scratch` is only a handle for the runtime, not a device address; the address
 // that kernels may use has to be asked for, with the device in question current.
 int fixed_scratch_for_current_device(void **out) {
   int dev = -1;
   QUIK_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return QUIK_ERR_UNSUPPORTED;
+  if (dev < 0 || dev >= kMaxDevices) return QUIK_ERR_UNSUPPORTED;
   std::lock_guard<std::mutex> lock(g_fixed_mutex);
   if (g_fixed_ptr[dev] == nullptr) {
     void *ptr = nullptr;
@@ -380,8 +390,8 @@ int fixed_scratch_for_current_device(void **out) {
 int quik_int4_matmul_fixed_scratch(const uint8_t *A, const uint8_t *B, int32_t *C, int M, int N, int K,
                                    void *stream) {
   if (M < 0 || N < 0 || K <= 0 || K % 32 != 0) return QUIK_ERR_SHAPE;
+  if (M == 0 || N == 0) return QUIK_OK;           // an empty product needs no scratch, whatever the other size
   if (quik_int4_matmul_scratch_bytes(M, N, K) > (size_t)QUIK_NOALLOC_SCRATCH_BYTES) return QUIK_ERR_TOO_LARGE;
-  if (M == 0 || N == 0) return QUIK_OK;
   if (!A || !B || !C) return QUIK_ERR_NULL;
   void *scratch = nullptr;
   int rc = fixed_scratch_for_current_device(&scratch);

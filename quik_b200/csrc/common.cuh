@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/quik_b200.h"
 
 namespace quik {
@@ -32,6 +34,40 @@ inline int check_launch(const char *what) {
 }
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- per-device launch state ----------------------------------------------------------------
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) and occupancy answers hold for the device that was
+// current when they were made.  A process may drive several GPUs (one layer per device, as the reference's
+// llama_multigpu does, experiments/llama.py:295-326) and several host threads, so every launcher keeps
+// this state per device ordinal behind a mutex.  One object per kernel instantiation (a function-local static).
+constexpr int kMaxDevices = 64;
+struct PerDeviceSmem {
+  std::mutex mu;
+  size_t opted[kMaxDevices] = {};     // bytes of dynamic shared memory opted in to on that device
+  int blocks_per_sm[kMaxDevices] = {};
+};
+// Makes sure `kern` may be launched with `smem` bytes of dynamic shared memory on the current device; when
+// `threads` > 0 also reports how many of its blocks fit on one SM (cached per device and size).
+template <typename Kern>
+int ensure_smem(PerDeviceSmem &st, Kern kern, size_t smem, int threads = 0, int *blocks_per_sm = nullptr) {
+  int dev = 0;
+  QUIK_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return QUIK_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(st.mu);
+  if (st.opted[dev] != smem + 1) {       // + 1: a kernel without dynamic shared memory is still recorded
+    if (smem > 48 * 1024)
+      QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int occ = 0;
+    if (threads > 0) {
+      QUIK_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, threads, smem));
+      if (occ < 1) return QUIK_ERR_UNSUPPORTED;
+    }
+    st.blocks_per_sm[dev] = occ;
+    st.opted[dev] = smem + 1;
+  }
+  if (blocks_per_sm) *blocks_per_sm = st.blocks_per_sm[dev];
+  return QUIK_OK;
+}
 
 // ---- launches with programmatic dependent launch ----------------------------------------------
 // The layer's kernels (quantizer, GEMM, weight-streaming engines) are launched so that a kernel may start
@@ -77,7 +113,9 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 // ---- device status word (bounded waits report here); lives in gemm_tcgen05.cu ---------------
 int device_status_read(int clear);   // synchronises the device
-void set_tile_n(int n);               // 0 = by shape, 128 or 256
+// tile shape the tcgen05 GEMM uses for an M x N problem of `kblocks` 128-byte k-blocks: CTAs per tile (1, 2) and width
+void choose_tile(int M, int N, int kblocks, int *ctas_out, int *bn_out);
+void set_tile_n(int n);               // 0 = by shape, else a multiple of 16 in [32, 256]
 int get_tile_n();
 void set_cta_pair(int mode);           // 0 = by shape, 1 = never, 2 = always
 int get_cta_pair();

@@ -2,7 +2,7 @@
 // shared-memory tiles, TMEM accumulators and a fused dequantize epilogue that can also add an
 // fp16/bf16 "outlier" GEMM (tcgen05.mma kind::f16 into a second TMEM accumulator).
 //
-// Computes, per 128 x BLOCK_N output tile (QUIK experiments/qlinear.py:122-145 in one launch):
+// Computes, per 128 x block_n output tile (QUIK experiments/qlinear.py:122-145 in one launch):
 //   acc_i[m,n] = sum_k A[m,k] * B[n,k]            (int8 operands, exact int32)   matmul.cu:98-136
 //   acc_f[m,n] = sum_j FA[m,j] * FB[n,j]          (fp16/bf16 operands, fp32)     qlinear.py:124
 //   out = T( acc_i * (s_m * sc_n) + ((z_m + shift * s_m) * wred_n + (acc_f + bias_n + y[m,n])) )
@@ -12,17 +12,21 @@
 // Structure (one persistent CTA per SM or one CTA pair per two SMs, 320 threads per CTA):
 //   warp 0    TMA producer: cp.async.bulk.tensor.2d loads of the A / B k-blocks (128 bytes of K
 //             per row, 128B swizzle) into a ring of shared-memory stages, completion on mbarriers.
-//   warp 1    allocates TMEM; one elected lane issues tcgen05.mma (M=128 or 256, N=BLOCK_N, K=32
+//   warp 1    allocates TMEM; one elected lane issues tcgen05.mma (M=128 or 256, N=block_n, K=32
 //             bytes) from shared-memory descriptors and commits each stage back to the producer.
 //   warps 2-9 epilogue: tcgen05.ld the accumulators (32 lanes x 32 columns per warp and step),
 //             apply the dequantize arithmetic in fp32 and store through a shared-memory transpose.
 // Outlier k-blocks (64 fp16 values = 128 bytes per row) travel through the same ring as the integer
 // k-blocks; TMEM holds two accumulator regions so the epilogue of tile i overlaps the MMAs of tile
 // i+1 (schedule in the comment above the kernel).
+// The tile width block_n is a launch parameter (any multiple of 16 up to the kernel's capacity CAP_N,
+// which fixes the shared-memory and TMEM plan): the host picks it per problem so that the tiles fill
+// whole waves of CTAs (choose_tile below).
 // Every wait is bounded: when a limit is hit the kernel records it in a device status word,
 // all roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -38,27 +42,29 @@ constexpr int BLOCK_M = 128;
 constexpr int STAGE_K_BYTES = 128;           // one 128B-swizzle row of K per stage
 constexpr int NUM_THREADS = 320;              // TMA warp + MMA warp + 8 epilogue warps
 constexpr int NUM_EPI_THREADS = 256;
-int g_tile_n = 0;                                             // 0 = choose by shape
-int g_cta_pair = 0;                                           // 0 = by shape, 1 = never, 2 = always
-unsigned long long *g_dbg = nullptr;                          // diagnostic counters (device memory), off by default
+// Process-wide tuning knobs (quik_config_set): plain words, meant to be set once before the layers run; a
+// launch reads each of them once.
+std::atomic<int> g_tile_n{0};                                 // 0 = choose by shape, else a multiple of 16 in [32, 256]
+std::atomic<int> g_cta_pair{0};                               // 0 = by shape, 1 = never, 2 = always
+std::atomic<unsigned long long *> g_dbg{nullptr};             // diagnostic counters (device memory), off by default
 
 // Shared-memory plan after the 1024-byte aligned ring of stages: 256 bytes of barriers etc. and the
 // per-warp epilogue vectors (rounded to 1024 together), then one output staging chunk per epilogue
 // warp (32 rows x 64 bytes).
 constexpr int EPI_BUF_BYTES = 32 * 64;
-constexpr int AUX_BYTES(int block_n) { return ((256 + 8 * 3 * (block_n / 2) * 4) + 1023) / 1024 * 1024; }
-constexpr int stage_bytes(int block_n, int ctas) { return (BLOCK_M + block_n / ctas) * STAGE_K_BYTES; }
+constexpr int AUX_BYTES(int cap_n) { return ((256 + 8 * 3 * (cap_n / 2) * 4) + 1023) / 1024 * 1024; }
+constexpr int stage_bytes(int cap_n, int ctas) { return (BLOCK_M + cap_n / ctas) * STAGE_K_BYTES; }
 constexpr int SMEM_LIMIT = 227 * 1024;
-constexpr int epi_bufs(int, int) { return 1; }
 // Ring depth: as many stages as fit (at most 8).
-constexpr int num_stages(int block_n, int ctas) {
-  const int n = (SMEM_LIMIT - 1024 - AUX_BYTES(block_n) - 8 * epi_bufs(block_n, ctas) * EPI_BUF_BYTES) /
-                stage_bytes(block_n, ctas);
+constexpr int num_stages(int cap_n, int ctas) {
+  const int n = (SMEM_LIMIT - 1024 - AUX_BYTES(cap_n) - 8 * EPI_BUF_BYTES) / stage_bytes(cap_n, ctas);
   return n > 8 ? 8 : n;
 }
 
 struct GemmParams {
   int M, N;
+  int block_n;                    // tile width: multiple of 16, <= CAP_N
+  int split_n;                    // columns of a tile that the first four epilogue warps take (multiple of 32 or block_n)
   int num_m_tiles, num_tiles;
   int int_kb, fp_kb;              // k-blocks per tile: integer (128 B each) and outlier (64 elems)
   uint32_t idesc_int, idesc_fp;   // tcgen05 instruction descriptors
@@ -117,7 +123,7 @@ __device__ __forceinline__ void store_row32(T *dst, bool vec, int ncols_left, co
 }
 // ---------------------------------------------------------------------------------------------
 // Work of one CTA = its tiles t_0, t_1, ... (tile index blockIdx.x + j * gridDim.x).  TMEM holds
-// two accumulator regions of BLOCK_N columns; tile j uses region j & 1 for BOTH of its products,
+// two accumulator regions (CAP_N columns apart); tile j uses region j & 1 for BOTH of its products,
 // one after the other:
 //   FP(t_j):  outlier k-blocks -> region (f32), drained by the epilogue warps, which round
 //             (product + bias) to T and park it in the tile's place in `out` (it stays in L2);
@@ -129,23 +135,24 @@ __device__ __forceinline__ void store_row32(T *dst, bool vec, int ncols_left, co
 // t_j in the shadow of INT(t_{j+1}): the tensor pipe never waits for an epilogue in steady state
 // although int32 and fp32 accumulators cannot share a region at the same time.
 //
-// CTAS == 2: two CTAs on neighbouring SMs (a cluster of 2) work on one 256 x BLOCK_N tile.  Each
+// CTAS == 2: two CTAs on neighbouring SMs (a cluster of 2) work on one 256 x block_n tile.  Each
 // loads its own 128 rows of A and only its half of the B rows, so a CTA moves a third less operand
 // data per multiply-accumulate than alone.  The leader (cluster rank 0) issues the MMAs for the pair
 // and owns the barriers that count loads and region releases; commits reach both CTAs.
-template <typename T, int BLOCK_N, bool HAS_FP, int CTAS>
+template <typename T, int CAP_N, bool HAS_FP, int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_fa, const __grid_constant__ CUtensorMap tmap_fb,
                     const GemmParams p) {
   constexpr int A_BYTES = BLOCK_M * STAGE_K_BYTES;
-  constexpr int B_ROWS = BLOCK_N / CTAS;                      // B rows this CTA loads per k-block
-  constexpr int B_BYTES = B_ROWS * STAGE_K_BYTES;
-  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr int STAGES = num_stages(BLOCK_N, CTAS);
-  constexpr int TMEM_ALLOC = 2 * BLOCK_N;                     // two accumulator regions
-  constexpr int HALF_N = BLOCK_N / 2;                         // columns per epilogue warp
+  constexpr int STAGE_BYTES = stage_bytes(CAP_N, CTAS);      // room for the widest tile; narrower ones use less of it
+  constexpr int STAGES = num_stages(CAP_N, CTAS);
+  constexpr int TMEM_ALLOC = 2 * CAP_N;                       // two accumulator regions, CAP_N columns apart
+  constexpr int HALF_CAP = CAP_N / 2;                         // most columns per epilogue warp
   constexpr int TILE_M = BLOCK_M * CTAS;
+  const int bn = p.block_n;
+  const int b_rows = bn / CTAS;                               // B rows this CTA loads per k-block
+  const uint32_t stage_tx = (uint32_t)(A_BYTES + b_rows * STAGE_K_BYTES) * CTAS;   // bytes of the whole pair
 
   extern __shared__ unsigned char smem_dyn[];
   // 128B-swizzled tiles need 1024-byte alignment
@@ -160,10 +167,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(fp_drained + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   // per-column epilogue vectors, one private copy per epilogue warp (no cross-warp barrier needed)
-  float *s_vec = reinterpret_cast<float *>(aux + 256);                 // [8][3][HALF_N], 16-byte aligned
+  float *s_vec = reinterpret_cast<float *>(aux + 256);                 // [8][3][HALF_CAP], 16-byte aligned
   // output staging: [8 warps][32 rows x 64 bytes], 1024-byte aligned
-  constexpr int EPI_BUFS = epi_bufs(BLOCK_N, CTAS);
-  unsigned char *s_out = tiles + STAGES * STAGE_BYTES + AUX_BYTES(BLOCK_N);
+  unsigned char *s_out = tiles + STAGES * STAGE_BYTES + AUX_BYTES(CAP_N);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -215,12 +221,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       auto feed = [&](int j, bool fp, int kb0, int kb1) {
         const int tile = unit + j * num_units;
         const int m0 = (tile % p.num_m_tiles) * TILE_M + rank * BLOCK_M;      // this CTA's rows of A
-        const int n0 = (tile / p.num_m_tiles) * BLOCK_N + rank * B_ROWS;      // this CTA's rows of B
+        const int n0 = (tile / p.num_m_tiles) * bn + rank * b_rows;           // this CTA's rows of B
         for (int kb = kb0; kb < kb1 && ok; ++kb) {
           if (!mbar_wait(smem_u32(empty_bar + stage), phase ^ 1, abort_flag)) { ok = false; break; }
           const uint32_t fb = smem_u32(full_bar + stage);
           const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
-          if (rank == 0) mbar_expect_tx(fb, STAGE_BYTES * CTAS);               // bytes of the whole pair
+          if (rank == 0) mbar_expect_tx(fb, stage_tx);
           if (fp) {
             tma_load_2d<CTAS>(sa, &tmap_fa, fb, kb * 64, m0);
             tma_load_2d<CTAS>(sa + A_BYTES, &tmap_fb, fb, kb * 64, n0);
@@ -249,7 +255,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       auto issue = [&](int j, bool fp, int kb0, int kb1) {
         const int r = j & 1;
         const uint32_t use_parity = (uint32_t)(j >> 1) & 1u;
-        const uint32_t d = tmem_base + r * BLOCK_N;
+        const uint32_t d = tmem_base + r * CAP_N;
         for (int kb = kb0; kb < kb1 && ok; ++kb) {
           if (kb == 0) {
             // the region must be free: after the previous tile's epilogue (outlier product, or
@@ -296,24 +302,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   } else {
     // ================= epilogue (warps 2..9) =================
-    // Warp (sub, half) owns rows [32*sub, 32*sub+32) x columns [HALF_N*half, +HALF_N) of the tile.
+    // Warp (sub, half) owns rows [32*sub, 32*sub+32) of the tile and the columns [cb, cb + cn): the first
+    // split_n columns for half 0, the rest for half 1.  It walks them 32 at a time; the last step of a range
+    // whose length is not a multiple of 32 holds 16 valid columns (`valid` below), the rest is ignored.
     const int e = warp - 2;
     const int sub = warp & 3;                 // TMEM lane quarter this warp may read
-    const int half = e >> 2;                  // which half of the tile's columns
-    float *s_scol = s_vec + e * 3 * HALF_N;
-    float *s_wred = s_scol + HALF_N;
-    float *s_bias = s_wred + HALF_N;
-    unsigned char *s_stage = s_out + e * (EPI_BUFS * EPI_BUF_BYTES);   // staging of one 32 x 32 output chunk
+    const int half = e >> 2;                  // which part of the tile's columns
+    const int cb = half ? p.split_n : 0;
+    const int cn = half ? bn - p.split_n : p.split_n;
+    const int cn32 = (cn + 31) & ~31;
+    float *s_scol = s_vec + e * 3 * HALF_CAP;
+    float *s_wred = s_scol + HALF_CAP;
+    float *s_bias = s_wred + HALF_CAP;
+    unsigned char *s_stage = s_out + e * EPI_BUF_BYTES;   // staging of one 32 x 32 output chunk
     bool ok = true;
     long long e_wait_fp = 0, e_wait_acc = 0, e_drain = 0, e_finish = 0;
 
     // Where the outlier product of (this warp, tile) is parked inside the tile's place in `out`.
-    // Every 32 x 32 chunk is parked inside its own 32-row x 64-byte block (so the final store of one
+    // Every full 32 x 32 chunk is parked inside its own 32-row x 64-byte block (so the final store of one
     // chunk never touches the parked data of another), but permuted: the jj-th 16-byte piece of lane
     // L goes to row 8*jj + L/4, piece L%4 of the block, so one warp instruction writes 8 rows x 64
     // contiguous bytes (whole sectors) instead of 32 rows x 16 bytes.  The same lane reads its pieces
-    // back from the same addresses; nobody else looks at them.  Sub-tiles that touch the matrix edge
-    // keep the plain row-per-lane layout with guards.
+    // back from the same addresses; nobody else looks at them.  Chunks that touch the matrix edge or hold
+    // fewer than 32 valid columns keep the plain row-per-lane layout with guards.
     auto parked_piece = [&](T *sub_base, int c0, int jj) -> uint4 * {   // sub_base = &out[first row of warp][n0]
       return reinterpret_cast<uint4 *>(sub_base + (size_t)(8 * jj + (lane >> 2)) * p.ldo + c0) + (lane & 3);
     };
@@ -322,11 +333,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     auto drain = [&](int j) {
       const int tile = unit + j * num_units;
       const int m0 = (tile % p.num_m_tiles) * TILE_M + rank * BLOCK_M + sub * 32;   // first row of this warp
-      const int n0 = (tile / p.num_m_tiles) * BLOCK_N + half * HALF_N;
+      const int n0 = (tile / p.num_m_tiles) * bn + cb;
+      const int lim = min(p.N - n0, cn);       // valid columns from n0 on (<= 0: none)
       const int r = j & 1;
       __syncwarp();
-      for (int c = lane; c < HALF_N; c += 32)
-        s_bias[c] = (n0 + c < p.N && p.bias) ? ldf<T>(p.bias, n0 + c) : 0.f;
+      for (int c = lane; c < cn32; c += 32)
+        s_bias[c] = (c < lim && p.bias) ? ldf<T>(p.bias, n0 + c) : 0.f;
       __syncwarp();
       const long long tw = clock64();
       const bool ready = mbar_wait(smem_u32(fp_full + r), (uint32_t)(j >> 1) & 1u, abort_flag);
@@ -335,24 +347,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       e_wait_fp += tw1 - tw;
       tc_fence_after();
       const int row = m0 + lane;
-      const bool interior = p.vec_out && m0 + 32 <= p.M && n0 + HALF_N <= p.N;
+      const bool rows_in = m0 + 32 <= p.M;
       T *sub_base = static_cast<T *>(p.out) + (size_t)m0 * p.ldo + n0;
-      const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + r * BLOCK_N + half * HALF_N;
+      const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + r * CAP_N + cb;
 #pragma unroll 1
-      for (int c0 = 0; c0 < HALF_N; c0 += 32) {
+      for (int c0 = 0; c0 < cn; c0 += 32) {
         uint32_t f[32];
         float o[32];
         __syncwarp();                          // tcgen05.ld is warp-collective
         tmem_ld32(taddr + c0, f);
         tmem_ld_wait();
+        const int valid = lim - c0;            // warp-uniform
+        if (valid <= 0) continue;
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(f[i]) + s_bias[c0 + i];
-        if (interior) {
+        if (p.vec_out && rows_in && valid >= 32) {
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) *parked_piece(sub_base, c0, jj) = pack8<T>(o + 8 * jj);
-        } else if (row < p.M && n0 + c0 < p.N) {
-          store_row32<T>(static_cast<T *>(p.out) + (size_t)row * p.ldo + n0 + c0, p.vec_out && n0 + c0 + 32 <= p.N,
-                         p.N - n0 - c0, o);
+        } else if (row < p.M) {
+          T *dst = static_cast<T *>(p.out) + (size_t)row * p.ldo + n0 + c0;
+          if (p.vec_out) {                     // valid is a multiple of 8 here
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj)
+              if (8 * jj < valid) reinterpret_cast<uint4 *>(dst)[jj] = pack8<T>(o + 8 * jj);
+          } else {
+            store_row32<T>(dst, false, valid, o);
+          }
         }
       }
       tc_fence_before();
@@ -364,13 +384,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     auto finish = [&](int j) {
       const int tile = unit + j * num_units;
       const int m0 = (tile % p.num_m_tiles) * TILE_M + rank * BLOCK_M + sub * 32;   // first row of this warp
-      const int n0 = (tile / p.num_m_tiles) * BLOCK_N + half * HALF_N;
+      const int n0 = (tile / p.num_m_tiles) * bn + cb;
+      const int lim = min(p.N - n0, cn);
       const int r = j & 1;
       if (p.mode == 1) {
         __syncwarp();                         // previous readers of the vectors are done
-        for (int c = lane; c < HALF_N; c += 32) {
+        for (int c = lane; c < cn32; c += 32) {
           const int col = n0 + c;
-          const bool in = col < p.N;
+          const bool in = c < lim;
           s_scol[c] = in ? ldf<T>(p.scale_col, col) : 0.f;
           s_wred[c] = (in && p.w_reduced) ? ldf<T>(p.w_reduced, col) : 0.f;
           s_bias[c] = (in && p.bias && !HAS_FP) ? ldf<T>(p.bias, col) : 0.f;   // with outliers the drain added it
@@ -379,20 +400,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
       const int row = m0 + lane;
       const bool row_ok = row < p.M;
-      const bool interior = p.vec_out && m0 + 32 <= p.M && n0 + HALF_N <= p.N;
+      const bool rows_in = m0 + 32 <= p.M;
       T *sub_base = static_cast<T *>(p.out) + (size_t)m0 * p.ldo + n0;
-      const T *my_row = static_cast<const T *>(p.out) + (size_t)row * p.ldo;
+      const T *my_row = static_cast<const T *>(p.out) + (size_t)row * p.ldo + n0;
       // The parked outlier product of the first 32 columns is fetched before waiting for the integer
       // product, the following ones one step ahead, so their L2 latency stays off the critical path.
       uint4 pk_next[4];
       auto prefetch_parked = [&](int c0) {
-        if (!HAS_FP || p.mode != 1) return;
-        if (interior) {
+        if (!HAS_FP || p.mode != 1 || !p.vec_out) return;
+        const int valid = lim - c0;
+        if (rows_in && valid >= 32) {
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) pk_next[jj] = *parked_piece(sub_base, c0, jj);
-        } else if (row_ok && p.vec_out && n0 + c0 + 32 <= p.N) {
+        } else if (row_ok) {
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) pk_next[jj] = reinterpret_cast<const uint4 *>(my_row + n0 + c0)[jj];
+          for (int jj = 0; jj < 4; ++jj)
+            if (8 * jj < valid) pk_next[jj] = reinterpret_cast<const uint4 *>(my_row + c0)[jj];
         }
       };
       prefetch_parked(0);
@@ -408,43 +431,43 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const float zrow = p.row_zero ? ldf<T>(p.row_zero, (size_t)row * p.row_stride) : 0.f;
         zs = fmaf(p.shift_value, srow, zrow);
       }
-      const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + r * BLOCK_N + half * HALF_N;
+      const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + r * CAP_N + cb;
 #pragma unroll 1
-      for (int c0 = 0; c0 < HALF_N; c0 += 32) {
+      for (int c0 = 0; c0 < cn; c0 += 32) {
         uint32_t v[32];
         uint4 pk[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) pk[i] = pk_next[i];
         __syncwarp();                          // tcgen05.ld is warp-collective: reconverge first
         tmem_ld32(taddr + c0, v);
-        if (c0 + 32 < HALF_N) prefetch_parked(c0 + 32);
+        if (c0 + 32 < cn) prefetch_parked(c0 + 32);
         tmem_ld_wait();
+        const int valid = lim - c0;            // warp-uniform
+        if (valid <= 0) continue;
         const int col0 = n0 + c0;
-        if (col0 >= p.N) continue;             // warp-uniform
-        const bool full_chunk = col0 + 32 <= p.N;
         const size_t off = (size_t)row * p.N + col0;
         if (p.mode == 0) {
           if (!row_ok) continue;
-          if (full_chunk && p.vec_out) {
+          if (p.vec_out) {                     // valid is a multiple of 4 here
             int4 *dst = reinterpret_cast<int4 *>(p.C + off);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              dst[i] = make_int4((int)v[4 * i], (int)v[4 * i + 1], (int)v[4 * i + 2], (int)v[4 * i + 3]);
+              if (4 * i < valid) dst[i] = make_int4((int)v[4 * i], (int)v[4 * i + 1], (int)v[4 * i + 2], (int)v[4 * i + 3]);
           } else {
             for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) p.C[off + i] = (int)v[i];
+              if (i < valid) p.C[off + i] = (int)v[i];
           }
           continue;
         }
         float o[32];   // addend first, result later
         if (HAS_FP) {
-          if (interior || (row_ok && full_chunk && p.vec_out)) {
+          if (p.vec_out) {
             const T *pe = reinterpret_cast<const T *>(pk);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = Traits<T>::to_float(pe[i]);
+            for (int i = 0; i < 32; ++i) o[i] = Traits<T>::to_float(pe[i]);   // pieces beyond `valid` are never stored
           } else {
             for (int i = 0; i < 32; ++i)
-              o[i] = (row_ok && col0 + i < p.N) ? Traits<T>::to_float(my_row[col0 + i]) : 0.f;
+              o[i] = (row_ok && i < valid) ? Traits<T>::to_float(my_row[c0 + i]) : 0.f;
           }
         } else {
 #pragma unroll
@@ -452,7 +475,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         if (p.y != nullptr && row_ok) {
           T yv[32];
-          load_row32<T>(static_cast<const T *>(p.y) + off, full_chunk && p.vec_y, p.N - col0, yv);
+          load_row32<T>(static_cast<const T *>(p.y) + off, valid >= 32 && p.vec_y, valid, yv);
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] += Traits<T>::to_float(yv[i]);
         }
@@ -479,7 +502,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             *reinterpret_cast<uint4 *>(s_stage + lane * 64 + ((jj ^ ((lane >> 1) & 3)) << 4)) = pack8<T>(o + 8 * jj);
           __syncwarp();
           const int pc = lane & 3;
-          const bool col_ok = col0 + 8 * pc + 8 <= p.N;
+          const bool col_ok = 8 * pc + 8 <= valid;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const int rr = 8 * k + (lane >> 2);
@@ -488,7 +511,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               *(reinterpret_cast<uint4 *>(static_cast<T *>(p.out) + (size_t)(m0 + rr) * p.ldo + col0) + pc) = piece;
           }
         } else if (row_ok) {
-          store_row32<T>(static_cast<T *>(p.out) + (size_t)row * p.ldo + col0, false, p.N - col0, o);
+          store_row32<T>(static_cast<T *>(p.out) + (size_t)row * p.ldo + col0, false, valid, o);
         }
       }
       tc_fence_before();
@@ -589,9 +612,9 @@ unsigned int *device_status_word() {
 
 namespace {
 
-constexpr size_t smem_bytes(int block_n, int ctas) {
-  return 1024 /*align slack*/ + (size_t)num_stages(block_n, ctas) * stage_bytes(block_n, ctas) + AUX_BYTES(block_n) +
-         8 * epi_bufs(block_n, ctas) * EPI_BUF_BYTES;
+constexpr size_t smem_bytes(int cap_n, int ctas) {
+  return 1024 /*align slack*/ + (size_t)num_stages(cap_n, ctas) * stage_bytes(cap_n, ctas) + AUX_BYTES(cap_n) +
+         8 * EPI_BUF_BYTES;
 }
 
 // Largest number of CTA pairs that can be resident at once (0 if pairs cannot be launched).
@@ -616,31 +639,100 @@ int max_pairs(Kern kern, size_t smem) {
   return n;
 }
 
-template <typename T, int BLOCK_N, bool HAS_FP, int CTAS>
+// Units (CTAs, or CTA pairs) of one kernel instantiation that are resident at once on the current device.
+// The shared-memory opt-in and the occupancy answer belong to a device, so they are kept per device ordinal.
+template <typename T, int CAP_N, bool HAS_FP, int CTAS>
+int resident_units(int *out) {
+  static std::mutex mu;
+  static int cached[kMaxDevices];       // 0 = not asked yet, -1 = cannot launch
+  int dev = 0;
+  QUIK_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return QUIK_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == 0) {
+    auto kern = gemm_tcgen05_kernel<T, CAP_N, HAS_FP, CTAS>;
+    constexpr size_t smem = smem_bytes(CAP_N, CTAS);
+    QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int n = CTAS == 1 ? num_sms() : max_pairs(kern, smem);
+    cached[dev] = n > 0 ? n : -1;
+  }
+  *out = cached[dev];
+  return QUIK_OK;
+}
+
+template <typename T, int CAP_N, bool HAS_FP, int CTAS>
 int launch_t(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tfa, const CUtensorMap &tfb,
              const GemmParams &p, cudaStream_t st) {
-  auto kern = gemm_tcgen05_kernel<T, BLOCK_N, HAS_FP, CTAS>;
-  constexpr size_t smem = smem_bytes(BLOCK_N, CTAS);
-  static int resident_units = -1;   // per instantiation: CTAs (one per SM) or CTA pairs that fit at once
-  if (resident_units < 0) {
-    QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    resident_units = CTAS == 1 ? num_sms() : max_pairs(kern, smem);
-  }
-  if (resident_units <= 0) return QUIK_ERR_UNSUPPORTED;
-  const int units = p.num_tiles < resident_units ? p.num_tiles : resident_units;
+  auto kern = gemm_tcgen05_kernel<T, CAP_N, HAS_FP, CTAS>;
+  constexpr size_t smem = smem_bytes(CAP_N, CTAS);
+  int resident = 0;
+  const int rc = resident_units<T, CAP_N, HAS_FP, CTAS>(&resident);
+  if (rc != QUIK_OK) return rc;
+  if (resident <= 0) return QUIK_ERR_UNSUPPORTED;
+  const int units = p.num_tiles < resident ? p.num_tiles : resident;
   LaunchCfg lc(dim3(CTAS * units), dim3(NUM_THREADS), smem, st, CTAS);
   QUIK_CUDA_TRY(cudaLaunchKernelEx(&lc.cfg, kern, ta, tb, tfa, tfb, p));
   return check_launch("gemm_tcgen05_kernel");
 }
 
+// ---- tile shape per problem -------------------------------------------------------------------
+// A launch is a number of waves of equally sized tiles over the resident units (CTAs or CTA pairs).  The time
+// of a tile is set by the slower of the tensor pipe (2 * block_n cycles per CTA and 128-byte k-block) and the
+// operand feed ((128 + block_n / ctas) rows of 128 bytes per CTA and k-block at kFeedBytesPerClk), so the
+// widest pair tile is the cheapest per multiply-accumulate, but a last wave that is mostly empty can cost more
+// than narrower tiles that fill their waves.  The model picks the (pair or single, block_n) with the smallest
+// waves x tile time; kFeedBytesPerClk and kTileFixedClk are fitted to measured sweeps over the Llama-2 shapes.
+constexpr double kFeedBytesPerClk = 43.0;
+constexpr double kTileFixedClk = 1500.0;
+
+double tile_cost(int M, int N, int kblocks, int ctas, int bn, int units) {
+  const int tile_m = BLOCK_M * ctas;
+  const long long tiles = (long long)((M + tile_m - 1) / tile_m) * ((N + bn - 1) / bn);
+  const long long waves = (tiles + units - 1) / units;
+  const double mma = 2.0 * bn;
+  const double feed = (BLOCK_M + bn / ctas) * (double)STAGE_K_BYTES / kFeedBytesPerClk;
+  return (double)waves * (kblocks * (mma > feed ? mma : feed) + kTileFixedClk);
+}
+
 }  // namespace
 
-void set_tile_n(int n) { g_tile_n = n; }
-int get_tile_n() { return g_tile_n; }
-void set_debug_counters(void *buf) { g_dbg = static_cast<unsigned long long *>(buf); }
-unsigned long long *get_debug_counters() { return g_dbg; }
-void set_cta_pair(int mode) { g_cta_pair = mode; }
-int get_cta_pair() { return g_cta_pair; }
+void choose_tile(int M, int N, int kblocks, int *ctas_out, int *bn_out) {
+  const int forced_n = g_tile_n.load(), pair_mode = g_cta_pair.load();
+  const int sms = num_sms();
+  const int n16 = (N + 15) & ~15;
+  double best = 0.0;
+  int best_ctas = 1, best_bn = 128;
+  bool have = false;
+  for (int ctas = 2; ctas >= 1; --ctas) {
+    if (ctas == 2 && (pair_mode == 1 || (pair_mode == 0 && M <= BLOCK_M))) continue;
+    if (ctas == 1 && pair_mode == 2) continue;
+    const int units = ctas == 2 ? sms / 2 : sms;
+    for (int bn = 256; bn >= 32; bn -= 16) {
+      int cand = bn;
+      if (forced_n) {
+        if (bn != 256) break;                       // one candidate only
+        cand = forced_n;
+      }
+      if (cand > n16) cand = n16 < 32 ? 32 : n16;   // a tile wider than the matrix only wastes columns
+      const double c = tile_cost(M, N, kblocks, ctas, cand, units);
+      if (!have || c < best) {
+        have = true;
+        best = c;
+        best_ctas = ctas;
+        best_bn = cand;
+      }
+    }
+  }
+  *ctas_out = best_ctas;
+  *bn_out = best_bn;
+}
+
+void set_tile_n(int n) { g_tile_n.store(n); }
+int get_tile_n() { return g_tile_n.load(); }
+void set_debug_counters(void *buf) { g_dbg.store(static_cast<unsigned long long *>(buf)); }
+unsigned long long *get_debug_counters() { return g_dbg.load(); }
+void set_cta_pair(int mode) { g_cta_pair.store(mode); }
+int get_cta_pair() { return g_cta_pair.load(); }
 
 int device_status_read(int clear) {
   unsigned int v = 0;
@@ -661,22 +753,21 @@ int launch_gemm_tcgen05(const int8_t *A, const int8_t *B, int M, int N, int K, c
   const bool has_fp = ep.mode == 1 && ep.fp_a != nullptr && ep.F > 0;
   if (has_fp && (ep.F % 8 != 0 || !aligned16(ep.fp_a) || !aligned16(ep.fp_b))) return QUIK_ERR_ALIGN;
 
-  // CTA pairs (256-row tiles) whenever there are at least two 128-row blocks of M; narrow tiles only
-  // for narrow outputs.
-  const int ctas = (g_cta_pair == 2 || (g_cta_pair == 0 && M > BLOCK_M)) ? 2 : 1;
-  const int tile_m = BLOCK_M * ctas;
-  const int m_tiles = (M + tile_m - 1) / tile_m;
-  int block_n = (N <= 128) ? 128 : 256;
-  if (ctas == 1 && N > 128 && m_tiles * ((N + 255) / 256) < num_sms()) block_n = 128;
-  if (g_tile_n == 128 || g_tile_n == 256) block_n = g_tile_n;
-
   GemmParams p{};
-  p.M = M;
-  p.N = N;
-  p.num_m_tiles = m_tiles;
-  p.num_tiles = m_tiles * ((N + block_n - 1) / block_n);
   p.int_kb = (K + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
   p.fp_kb = has_fp ? (ep.F + 63) / 64 : 0;
+  int ctas = 1, block_n = 128;
+  choose_tile(M, N, p.int_kb + p.fp_kb, &ctas, &block_n);
+  const int tile_m = BLOCK_M * ctas;
+  const int m_tiles = (M + tile_m - 1) / tile_m;
+  const int cap_n = block_n <= 128 ? 128 : 256;
+
+  p.M = M;
+  p.N = N;
+  p.block_n = block_n;
+  p.split_n = ((block_n / 2 + 31) & ~31) < block_n ? ((block_n / 2 + 31) & ~31) : block_n;
+  p.num_m_tiles = m_tiles;
+  p.num_tiles = m_tiles * ((N + block_n - 1) / block_n);
   p.idesc_int = make_idesc(2, 1, tile_m, block_n);                              // S32 accumulate, signed 8-bit operands
   p.idesc_fp = make_idesc(1, ep.dtype == QUIK_BF16 ? 1 : 0, tile_m, block_n);   // F32 accumulate, F16 / BF16 operands
   p.mode = ep.mode;
@@ -701,7 +792,7 @@ int launch_gemm_tcgen05(const int8_t *A, const int8_t *B, int M, int N, int K, c
   if (ep.mode == 0) p.vec_out = (N % 4 == 0) && aligned16(ep.C);
   else p.vec_out = (N % 8 == 0) && (p.ldo % 8 == 0) && aligned16(ep.out);
   p.vec_y = ep.y && (N % 8 == 0) && aligned16(ep.y);
-  p.dbg = g_dbg;
+  p.dbg = g_dbg.load();
 
   CUtensorMap ta, tb, tfa, tfb;
   int rc;
@@ -717,7 +808,7 @@ int launch_gemm_tcgen05(const int8_t *A, const int8_t *B, int M, int N, int K, c
   }
 #define QUIK_LAUNCH_C(T, C)                                                                \
   do {                                                                                     \
-    if (block_n == 256) {                                                                  \
+    if (cap_n == 256) {                                                                    \
       return has_fp ? launch_t<T, 256, true, C>(ta, tb, tfa, tfb, p, st)                   \
                     : launch_t<T, 256, false, C>(ta, tb, tfa, tfb, p, st);                 \
     }                                                                                      \

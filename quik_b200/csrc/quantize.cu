@@ -283,17 +283,12 @@ int launch_asym_rows_nc(const void *src, int rows, int cols, const void *int_idx
   const size_t smem = nbuf * row_bytes;
   if (smem > 200 * 1024) return QUIK_ERR_UNSUPPORTED;
   auto kern = asym_quantize_row_kernel<T, BITS, WIDE, IdxT, NC, NTHR>;
-  // attribute and occupancy are looked up once per (instantiation, shared-memory size)
-  static size_t cached_smem = 0;
-  static int cached_per_sm = 0;
-  if (cached_smem != smem || cached_per_sm < 1) {
-    if (smem > 48 * 1024)
-      QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    int occ = 0;
-    QUIK_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NTHR, smem));
-    if (occ < 1) return QUIK_ERR_UNSUPPORTED;
-    cached_smem = smem;
-    cached_per_sm = occ;
+  // shared-memory opt-in and occupancy: once per (instantiation, device, shared-memory size)
+  static PerDeviceSmem state;
+  int cached_per_sm = 0;
+  {
+    const int rc = ensure_smem(state, kern, smem, NTHR, &cached_per_sm);
+    if (rc != QUIK_OK) return rc;
   }
   const int grid = min(rows, num_sms() * cached_per_sm);
   const int vec_load = (cols % 8 == 0) && aligned16(src);

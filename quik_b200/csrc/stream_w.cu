@@ -455,10 +455,10 @@ template <typename T, int BITS, int NTOK>
 int launch_t(const CUtensorMap &tw, const CUtensorMap &tx, const CUtensorMap &tfw, const CUtensorMap &tfx,
              const StreamParams &p, int slabs, cudaStream_t st) {
   auto kern = stream_w_kernel<T, BITS, NTOK>;
-  static bool configured = false;
-  if (!configured) {
-    QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SwCfg<NTOK>::SMEM));
-    configured = true;
+  static PerDeviceSmem state;
+  {
+    const int rc = ensure_smem(state, kern, SwCfg<NTOK>::SMEM);
+    if (rc != QUIK_OK) return rc;
   }
   LaunchCfg lc(dim3(slabs * p.splits), dim3(SW_THREADS), SwCfg<NTOK>::SMEM, st, p.splits);
   QUIK_CUDA_TRY(cudaLaunchKernelEx(&lc.cfg, kern, tw, tx, tfw, tfx, p));

@@ -325,10 +325,10 @@ template <typename T, int BITS>
 int launch_t(const CUtensorMap &tw, const CUtensorMap &tx, const CUtensorMap &tfw, const CUtensorMap &tfx,
              const MmaStreamParams &p, int slabs, cudaStream_t st) {
   auto kern = stream_w_mma_kernel<T, BITS>;
-  static bool configured = false;
-  if (!configured) {
-    QUIK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM_SMEM));
-    configured = true;
+  static PerDeviceSmem state;
+  {
+    const int rc = ensure_smem(state, kern, SM_SMEM);
+    if (rc != QUIK_OK) return rc;
   }
   LaunchCfg lc(dim3(slabs * p.splits), dim3(SM_THREADS2), SM_SMEM, st, p.splits);
   QUIK_CUDA_TRY(cudaLaunchKernelEx(&lc.cfg, kern, tw, tx, tfw, tfx, p));

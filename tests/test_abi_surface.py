@@ -40,7 +40,10 @@ def test_host_only_entry_points():
     assert lib.quik_config_get(_lib.CFG_GEMM_ENGINE) == _lib.ENGINE_MMA_SYNC
     assert lib.quik_config_set(_lib.CFG_GEMM_ENGINE, 0) == 0
     assert lib.quik_config_set(_lib.CFG_GEMM_ENGINE, 9) != 0
-    assert lib.quik_config_set(_lib.CFG_TILE_N, 192) != 0
+    assert lib.quik_config_set(_lib.CFG_TILE_N, 192) == 0          # any multiple of 16 from 32 to 256
+    assert lib.quik_config_get(_lib.CFG_TILE_N) == 192
+    assert lib.quik_config_set(_lib.CFG_TILE_N, 200) != 0 and lib.quik_config_set(_lib.CFG_TILE_N, 272) != 0
+    assert lib.quik_config_set(_lib.CFG_TILE_N, 0) == 0
     # argument validation happens before any CUDA call
     assert lib.quik_asym_quantize(None, 0, 4, 64, None, 56, None, 8, 3, None, None, None, None) == -2
     assert lib.quik_asym_quantize(None, 0, 4, 64, None, 55, None, 8, 4, None, None, None, None) == -3

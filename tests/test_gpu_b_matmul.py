@@ -11,7 +11,13 @@ pytestmark = pytest.mark.gpu
 # (id, engine, tile width, CTA-pair mode: 1 = single CTAs, 2 = CTA pairs)
 ENGINES = [("mma_sync", _lib.ENGINE_MMA_SYNC, 0, 0), ("tcgen05_auto", _lib.ENGINE_TCGEN05, 0, 0),
            ("tcgen05_1cta_n128", _lib.ENGINE_TCGEN05, 128, 1), ("tcgen05_1cta_n256", _lib.ENGINE_TCGEN05, 256, 1),
-           ("tcgen05_pair_n128", _lib.ENGINE_TCGEN05, 128, 2), ("tcgen05_pair_n256", _lib.ENGINE_TCGEN05, 256, 2)]
+           ("tcgen05_pair_n128", _lib.ENGINE_TCGEN05, 128, 2), ("tcgen05_pair_n256", _lib.ENGINE_TCGEN05, 256, 2),
+           # tile widths that are not a power of two (chosen per problem against partial waves); 240, 208, 176,
+           # 144 and 48 end an epilogue warp's column range with a 16-column step
+           ("tcgen05_pair_n240", _lib.ENGINE_TCGEN05, 240, 2), ("tcgen05_pair_n224", _lib.ENGINE_TCGEN05, 224, 2),
+           ("tcgen05_pair_n208", _lib.ENGINE_TCGEN05, 208, 2), ("tcgen05_1cta_n176", _lib.ENGINE_TCGEN05, 176, 1),
+           ("tcgen05_pair_n144", _lib.ENGINE_TCGEN05, 144, 2), ("tcgen05_1cta_n96", _lib.ENGINE_TCGEN05, 96, 1),
+           ("tcgen05_pair_n48", _lib.ENGINE_TCGEN05, 48, 2)]
 
 
 @pytest.fixture(params=ENGINES, ids=[e[0] for e in ENGINES])
@@ -38,12 +44,34 @@ def test_int8_matmul_exact(engine, M, N, K):
     g = torch.Generator().manual_seed(M + N + K)
     a = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8)
     b = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8)
-    # canary-padded output: the kernel must write exactly [M, N]
     c = quik.matmul.int8Matmul(a.to(dev()), b.to(dev()))
     ref = kp.int8_matmul(a, b)
     assert torch.equal(c.cpu(), ref)
     c2 = quik.matmul.int8Matmul(a.to(dev()), b.to(dev()))
     assert torch.equal(c2, c)
+
+
+POISON = 0x5A5A5A5A
+
+
+@pytest.mark.parametrize("M,N,K", [(129, 260, 256), (300, 520, 1024), (17, 4100, 176), (256, 512, 512), (1, 8, 16)])
+def test_int8_matmul_writes_only_its_output(engine, M, N, K):
+    """The int32 result sits in the middle of a poisoned slab (16 rows before and after, called through the C ABI
+    with a pointer into the slab): every element of [M, N] is written and nothing around it is touched.  Stands in
+    for a memory checker on the ragged-edge stores of the tiled kernels."""
+    from quik_b200._lib import check, load, ptr
+    g = torch.Generator().manual_seed(M * 7 + N)
+    a = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8)
+    b = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8)
+    pad = 16
+    slab = torch.full((M + 2 * pad, N), POISON, dtype=torch.int32, device=dev())
+    c = slab[pad:pad + M]
+    ad, bd = a.to(dev()), b.to(dev())
+    check(load().quik_int8_matmul(ptr(ad), ptr(bd), c.data_ptr(), M, N, K, torch.cuda.current_stream().cuda_stream),
+          "quik_int8_matmul")
+    torch.cuda.synchronize()
+    assert torch.equal(c.cpu(), kp.int8_matmul(a, b))
+    assert bool((slab[:pad] == POISON).all()) and bool((slab[pad + M:] == POISON).all())
 
 
 @pytest.mark.parametrize("M,N,K", [(512, 32, 512), (64, 136, 3840), (2048, 512, 4096), (5, 24, 64)])

@@ -50,6 +50,42 @@ def test_fused_forward_matches_oracle(dtype, M, K, N, F, bits):
     assert_device_clean()
 
 
+@pytest.mark.parametrize("col_pad", [8, 3])
+@pytest.mark.parametrize("tile,pair", [(0, 0), (240, 2), (144, 2), (176, 1)])
+@pytest.mark.parametrize("M,K,N,F,bits", [(300, 1088, 520, 64, 4), (129, 1088, 264, 64, 8), (257, 608, 1000, 32, 4),
+                                          (16, 1088, 520, 64, 4), (100, 1088, 520, 64, 8)])
+def test_fused_layer_writes_only_its_columns(M, K, N, F, bits, tile, pair, col_pad):
+    """The layer's output is a window of a poisoned slab (rows and columns of padding on every side, handed over as
+    `out_buffer` with a row pitch wider than N): the window equals the plain forward bit for bit and the padding is
+    untouched.  col_pad = 8 keeps the window 16-byte aligned (vector stores, parked outlier products in the
+    permuted layout), col_pad = 3 does not (scalar stores); the tile widths end a warp's column range with a
+    16-column step.  Covers the ragged-edge stores and the parked-tile writes of the tiled kernel and the stores of
+    the weight-streaming engines (16 and 100 tokens)."""
+    case = make_layer("t", M, K, N, bits, F=F, seed=M + N, device=dev(), clip=False)
+    row_pad = 5
+    poison = -1234.0
+    try:
+        _lib.set_tile_n(tile)
+        _lib.set_cta_pair(pair)
+        want = case.module(case.x.unsqueeze(0))[0].clone()
+        slab = torch.full((M + 2 * row_pad, N + 2 * col_pad), poison, dtype=torch.float16, device=dev())
+        window = slab[row_pad:row_pad + M, col_pad:col_pad + N]
+        case.module.out_buffer = window
+        got = case.module(case.x.unsqueeze(0))[0]
+        assert got.data_ptr() == window.data_ptr()
+        torch.cuda.synchronize()
+    finally:
+        case.module.out_buffer = None
+        _lib.set_tile_n(0)
+        _lib.set_cta_pair(0)
+    assert_device_clean()
+    assert torch.equal(window, want)
+    border = slab.clone()
+    border[row_pad:row_pad + M, col_pad:col_pad + N] = poison
+    assert bool((border == poison).all()), "the layer wrote outside its [M, N] window"
+    assert rel_rms_err(want.cpu(), _oracle_out(case, round_y=False)) < TOL_RMS
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("M,K,N,F,bits", [
     (16, 256, 128, 0, 4), (16, 1280, 128, 256, 8), (1, 4352, 512, 256, 4), (16, 4352, 264, 256, 4), (7, 11264, 256, 256, 8),

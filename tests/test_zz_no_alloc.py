@@ -5,11 +5,14 @@ quik_int4_matmul_fixed_scratch serves hosts that cannot call cudaMalloc when the
 allocation may imply): its scratch is a fixed array inside the library instead of caller memory.
 The test drives it through the C ABI, twice in a row with different operands and shapes -- the
 second call finds the first call's leftovers in the shared array -- and demands the very same int32
-results as the regular entry point, plus a clean refusal of sizes beyond the fixed area.
+results as the regular entry point and as the CPU oracle's exact integer product, plus a clean refusal
+of sizes beyond the fixed area.  Where a second GPU is present the small case is repeated there: the
+array's device address is looked up per device.
 """
 import pytest
 import torch
 
+from oracle import kernel_path as kp
 from quik_b200 import _lib
 from quik_b200._lib import load, ptr
 
@@ -47,10 +50,34 @@ def test_fixed_scratch_matches_regular_entry_point_twice():
     b2 = torch.randint(0, 256, (136, 256), generator=g, dtype=torch.uint8).to(dev)
     got2, want2 = _both(lib, a2, b2)
     assert torch.equal(got2, want2)
+    # both against the oracle's exact integer product of the same packed operands
+    assert torch.equal(got1.cpu(), kp.int4_matmul(a1.cpu(), b1.cpu()))
+    assert torch.equal(got2.cpu(), kp.int4_matmul(a2.cpu(), b2.cpu()))
     # and the first problem again gives the first answer again
     got3, _ = _both(lib, a1, b1)
     assert torch.equal(got3, want1)
     assert _lib.device_status() == 0
+
+
+def test_fixed_scratch_on_a_second_device():
+    """The fixed array exists once per GPU; its address is looked up with that GPU current."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    lib = load()
+    g = torch.Generator().manual_seed(5)
+    a = torch.randint(0, 256, (77, 256), generator=g, dtype=torch.uint8)
+    b = torch.randint(0, 256, (136, 256), generator=g, dtype=torch.uint8)
+    want = kp.int4_matmul(a, b)
+    for d in (1, 0):
+        with torch.cuda.device(d):
+            got, same = _both(lib, a.to(f"cuda:{d}"), b.to(f"cuda:{d}"))
+            assert torch.equal(got.cpu(), want) and torch.equal(same.cpu(), want)
+
+
+def test_fixed_scratch_empty_problem_is_ok_whatever_the_other_size():
+    lib = load()
+    rc = lib.quik_int4_matmul_fixed_scratch(None, None, None, 0, 1 << 20, 4096, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
 
 
 def test_fixed_scratch_rejects_sizes_beyond_its_area():
