@@ -198,9 +198,9 @@ def int8_peaks(peaks, lib_int8):
 
 
 # ---------------------------------------------------------------------------------------------
-def cpu_fake_quant_baseline(shapes, tokens, steps, warmup, seed=0):
-    """The reference's torch fake-quant simulation (experiments/quant_sim.py ActQuantWrapper around
-    nn.Linear with RTN-quantized weights), ported in oracle/fakequant.py, timed on the host cores."""
+def cpu_fake_quant_layers(shapes, tokens, seed=0):
+    """The layers of the step as the reference's torch fake-quant simulation (experiments/quant_sim.py ActQuantWrapper
+    around nn.Linear with RTN-quantized weights), ported in oracle/fakequant.py, with their seeded inputs."""
     from oracle import fakequant
     from quik_b200 import workloads
     torch.set_num_threads(os.cpu_count() or 1)
@@ -222,6 +222,11 @@ def cpu_fake_quant_baseline(shapes, tokens, steps, warmup, seed=0):
         layer.weight = w
         layers.append((layer, x.half()))
         ops += 2.0 * tokens * N * K
+    return layers, ops
+
+
+def cpu_fake_quant_time(layers, ops, tokens, steps, warmup):
+    """Times `steps` passes over the layers on the host cores after `warmup` passes."""
     times = []
     with torch.no_grad():
         for i in range(warmup + steps):
@@ -233,7 +238,7 @@ def cpu_fake_quant_baseline(shapes, tokens, steps, warmup, seed=0):
                 times.append(dt)
     mean = sum(times) / len(times)
     return {"value": ops / mean / 1e12, "unit": "TOPS", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"all {tokens} tokens of the workload per layer, all {len(shapes)} layers, "
+            "sample": f"all {tokens} tokens of the workload per layer, all {len(layers)} layers, "
                       f"{steps} timed passes after {warmup} warm-up (oracle/fakequant.py on "
                       f"{os.cpu_count()} host cores)", "ms_per_step": mean * 1e3}
 
@@ -243,13 +248,17 @@ def run_reference_arm(args, shapes, config):
     if rank != 0:
         return
     # one pass over the full workload is seconds of CPU work: the arm keeps the GPU arm's warm-up and step counts as
-    # long as the whole run stays within about four minutes, else it shortens them and says so
-    probe = cpu_fake_quant_baseline(shapes, args.tokens, 1, 1)
+    # long as the whole run stays within about four minutes, else it shortens them and says so in `sample`
+    layers, ops = cpu_fake_quant_layers(shapes, args.tokens)
+    probe = cpu_fake_quant_time(layers, ops, args.tokens, 1, 1)
     per_pass = probe["ms_per_step"] * 1e-3
     budget = 240.0
-    warm = max(1, min(max(args.warmup, 3), int(budget * 0.2 / per_pass)))
+    want_warm = max(args.warmup, 3)
+    warm = max(1, min(want_warm, int(budget * 0.2 / per_pass)))
     steps = max(1, min(args.steps, int(budget * 0.8 / per_pass)))
-    base = cpu_fake_quant_baseline(shapes, args.tokens, steps, warm)
+    base = cpu_fake_quant_time(layers, ops, args.tokens, steps, warm)
+    if steps < args.steps or warm < want_warm:
+        base["sample"] += f"; shortened from {args.steps} steps / {want_warm} warm-up to stay within a few minutes"
     line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "TOPS", "n_gpus": args.gpus,
             "steps": steps, "warmup": warm, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": config,
@@ -433,7 +442,7 @@ def quantizer_times(wl, iters=30):
     torch.cuda.synchronize()
     total_bytes, total_ms = 0.0, 0.0
     for i, (c, m) in enumerate(zip(wl.cases, mods)):
-        ms = statistics.median([a.elapsed_time(b) for a, b in evs[i]])
+        ms = statistics.fmean([a.elapsed_time(b) for a, b in evs[i]])
         nbytes = c.M * c.K * 2 + c.M * (c.K - c.F) + c.M * c.F * 2 + c.M * 4     # X in; codes (one per byte), outliers, meta out
         res[c.name] = {"us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9}
         total_bytes += nbytes
@@ -476,7 +485,7 @@ def measure_workload(args, wl, peaks, i8peaks, rank, world, dev, sync_all, sampl
         if id(c.module) not in per:
             continue
         ts = per[id(c.module)][1]
-        med = statistics.median(ts)
+        med = statistics.fmean(ts)                         # event timestamps tick in ~2 us steps: the mean resolves finer than the median
         ops = 2.0 * M * c.N * c.K                          # this rank's shard
         gemm_ms += med
         gemm_ops += ops
@@ -504,7 +513,7 @@ def measure_workload(args, wl, peaks, i8peaks, rank, world, dev, sync_all, sampl
                     "frac_of_nominal_4500": achieved / 4500.0,
                     "per_layer": per_layer,
                     "timing": f"CUDA events around each launch of the kernel over {eager_steps} eagerly launched steps "
-                              f"right after the graph-replayed region; median per layer"}
+                              f"right after the graph-replayed region; mean per layer"}
     else:
         # few tokens: the layer is bound by reading its weights once; algorithmic bytes of the launch over its duration
         wbytes = {c.name: c.N * (c.K - c.F) * c.bits / 8 + c.N * c.F * 2 + 4 * c.N + c.M * (c.K - c.F) + 2 * c.M * c.F
@@ -525,7 +534,7 @@ def measure_workload(args, wl, peaks, i8peaks, rank, world, dev, sync_all, sampl
                     "whole_step_note": f"graph replay over {len(wl.sets)} rotating weight sets "
                                        f"({len(wl.sets) * sum(wbytes.values()) / 1e6:.0f} MB, L2 is {L2_BYTES / 1e6:.0f} MB); "
                                        f"algorithmic bytes of the step (weights, X, outputs) / step time, quantizers included",
-                    "timing": f"CUDA events around each launch over {eager_steps} eagerly launched steps, median per layer"}
+                    "timing": f"CUDA events around each launch over {eager_steps} eagerly launched steps, mean per layer"}
 
     q_roof = None
     if world == 1:
@@ -533,7 +542,7 @@ def measure_workload(args, wl, peaks, i8peaks, rank, world, dev, sync_all, sampl
         q_roof = {"bound": "hbm", "achieved": qbytes / (qms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                   "frac": (qbytes / (qms * 1e-3) / 1e9) / peaks["hbm_gbs"], "kernel": "asym_quantize_row_kernel",
                   "per_layer": qres, "us_per_step": qms * 1e3,
-                  "timing": "CUDA events around each launch, the step's layers in turn, median of 30"}
+                  "timing": "CUDA events around each launch, the step's layers in turn, mean of 30"}
 
     e2e = None
     if want_e2e and not args.no_e2e:
@@ -875,7 +884,8 @@ def main():
         if args.dtype == "fp16":
             block = decoder_block_record(dev)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu_base = cpu_fake_quant_baseline(shapes, M, 2, 1)
+        cpu_layers, cpu_ops = cpu_fake_quant_layers(shapes, M)
+        cpu_base = cpu_fake_quant_time(cpu_layers, cpu_ops, M, 2, 1)
         cpu_base = {k: cpu_base[k] for k in ("value", "unit", "cores", "kind", "sample")}
 
     if rank == 0:
