@@ -41,9 +41,10 @@ extern "C" {
 
 /* ---- integer-GEMM engines (quik_config_set(QUIK_CFG_GEMM_ENGINE, ...)) -------------------- */
 #define QUIK_CFG_GEMM_ENGINE   1
-#define QUIK_ENGINE_AUTO       0    /* tcgen05 + TMA + TMEM where the shape allows, else mma.sync */
-#define QUIK_ENGINE_TCGEN05    1
-#define QUIK_ENGINE_MMA_SYNC   2
+#define QUIK_ENGINE_AUTO       0    /* the fastest engine the shape allows (tcgen05 with the token operand in tensor memory) */
+#define QUIK_ENGINE_TCGEN05    1    /* tcgen05, both operands read from shared memory                              */
+#define QUIK_ENGINE_MMA_SYNC   2    /* legacy mma.sync tensor path (comparison engine)                            */
+#define QUIK_ENGINE_TCGEN05_TS 3    /* tcgen05, token operand moved (4-bit codes: widened) into tensor memory      */
 /* Output-tile width of the tcgen05 engine: 0 = chosen per problem (so that the tiles fill whole waves of CTAs),
  * else a multiple of 16 from 32 to 256. */
 #define QUIK_CFG_TILE_N        2
@@ -69,7 +70,7 @@ const char *quik_last_cuda_error(void);
  * launch is safe but each of those launches sees either the old or the new value. */
 int quik_config_set(int key, int value);
 int quik_config_get(int key);
-/* Diagnostics: the tile shape the tcgen05 engine would use on the current device for M tokens, N output channels,
+/* Diagnostics: the tile shape the selected tcgen05 engine would use on the current device for M tokens, N output channels,
  * K_int integer and F outlier columns: CTAs per tile (1, or 2 = a CTA pair working on 256 rows) and tile width.
  * No reference counterpart (CUTLASS fixes one threadblock shape per kernel, src/matmul/matmul.cu:24-34). */
 int quik_gemm_plan(int M, int N, int K_int, int F, int *ctas, int *block_n);
@@ -204,10 +205,15 @@ int quik_fused_dequantize(const void *A, const void *B, int bits,
  *   out      [M, N] dtype
  * 4-bit layers choose the engine by the operand layout:
  *   q one per byte, w one per byte   tensor-core GEMM (any M);
+ *   q packed,       w one per byte   tensor-core GEMM whose token operand is widened on chip on its way into tensor
+ *                                    memory (any M, K_int % 32 == 0; engine AUTO or TCGEN05_TS);
  *   q one per byte, w packed         weight streaming on tcgen05 (M <= QUIK_STREAM_M_MAX, K_int % 32 == 0): the
  *                                    packed weights are widened on chip on their way to the tensor cores;
  *   q packed,       w packed         weight streaming on mma.sync, direct loads or TMA ring by QUIK_CFG_SMALL_M
  *                                    (M <= QUIK_SMALL_M_MAX, K_int % 32 == 0).
+ * The tensor-core engines use `out` as scratch while they run (the rounded outlier product + bias is parked there
+ * before the dequantize step, as the reference's F.linear output is rounded, experiments/qlinear.py:124): `out` must
+ * not alias any input.
  * K_int % 16 == 0, F % 8 == 0. */
 #define QUIK_SMALL_M_MAX 16
 /* most tokens the tcgen05 weight-streaming engine takes (q one code per byte, w in storage format) */

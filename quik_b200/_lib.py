@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libquik_b200.so")
 QUIK_OK = 0
 F16, BF16 = 0, 1
 CFG_GEMM_ENGINE, CFG_TILE_N, CFG_SMALL_M, CFG_CTA_PAIR, CFG_PDL = 1, 2, 3, 4, 5
-ENGINE_AUTO, ENGINE_TCGEN05, ENGINE_MMA_SYNC = 0, 1, 2
+ENGINE_AUTO, ENGINE_TCGEN05, ENGINE_MMA_SYNC, ENGINE_TCGEN05_TS = 0, 1, 2, 3
 SMALL_M_MAX = 16       # most tokens of the mma.sync weight-streaming engines
 STREAM_M_MAX = 128     # most tokens of the tcgen05 weight-streaming engine
 
@@ -115,6 +115,11 @@ def set_engine(engine: int) -> None:
     check(load().quik_config_set(CFG_GEMM_ENGINE, engine), "quik_config_set")
 
 
+def config_get(key: int) -> int:
+    """Current value of a process-wide setting (the library's own word, not a Python-side copy)."""
+    return load().quik_config_get(key)
+
+
 def set_tile_n(n: int) -> None:
     check(load().quik_config_set(CFG_TILE_N, n), "quik_config_set")
 
@@ -125,17 +130,13 @@ def set_cta_pair(mode: int) -> None:
 
 
 SMALL_M_OFF, SMALL_M_AUTO, SMALL_M_MMA_SYNC, SMALL_M_TCGEN05, SMALL_M_TMA_MMA = 0, 1, 2, 3, 4
-small_m_mode = SMALL_M_AUTO      # mirror of QUIK_CFG_SMALL_M, read by MixedQLinear on every call
 
 
 def set_small_m(mode) -> None:
     """Engine for layers with at most SMALL_M_MAX tokens: 0 = none (tensor-core GEMM on widened weights),
     1 / True = weight streaming, engine by layer size, 2 = mma.sync fed by direct loads, 3 = tcgen05 fed by a TMA
     ring, 4 = mma.sync fed by a TMA ring."""
-    global small_m_mode
-    mode = int(mode)
-    check(load().quik_config_set(CFG_SMALL_M, mode), "quik_config_set")
-    small_m_mode = mode
+    check(load().quik_config_set(CFG_SMALL_M, int(mode)), "quik_config_set")
 
 
 def set_pdl(on: bool) -> None:

@@ -40,8 +40,10 @@ static bool dtype_ok(int dtype) { return dtype == QUIK_F16 || dtype == QUIK_BF16
 
 static int run_int8_gemm(const int8_t *A, const int8_t *B, int M, int N, int K, const Epilogue &ep,
                          cudaStream_t st) {
-  if (g_engine == QUIK_ENGINE_MMA_SYNC) return launch_gemm_mma_sync(A, B, M, N, K, ep, st);
-  return launch_gemm_tcgen05(A, B, M, N, K, ep, st);
+  const int engine = g_engine.load();
+  if (engine == QUIK_ENGINE_MMA_SYNC) return launch_gemm_mma_sync(A, B, M, N, K, ep, st);
+  if (engine == QUIK_ENGINE_TCGEN05) return launch_gemm_tcgen05(A, B, M, N, K, ep, st);
+  return launch_gemm_tcgen05_ts(A, 0, B, M, N, K, ep, st);
 }
 
 }  // namespace quik
@@ -73,7 +75,7 @@ const char *quik_last_cuda_error(void) { return g_err; }
 
 int quik_config_set(int key, int value) {
   if (key == QUIK_CFG_GEMM_ENGINE) {
-    if (value < QUIK_ENGINE_AUTO || value > QUIK_ENGINE_MMA_SYNC) return QUIK_ERR_UNSUPPORTED;
+    if (value < QUIK_ENGINE_AUTO || value > QUIK_ENGINE_TCGEN05_TS) return QUIK_ERR_UNSUPPORTED;
     g_engine = value;
     return QUIK_OK;
   }
@@ -112,7 +114,9 @@ int quik_device_status(int clear) { return device_status_read(clear); }
 
 int quik_gemm_plan(int M, int N, int K_int, int F, int *ctas, int *block_n) {
   if (M <= 0 || N <= 0 || K_int <= 0 || F < 0 || !ctas || !block_n) return QUIK_ERR_SHAPE;
-  choose_tile(M, N, (K_int + 127) / 128 + (F + 63) / 64, ctas, block_n);
+  const int kblocks = (K_int + 127) / 128 + (F + 63) / 64;
+  if (g_engine.load() == QUIK_ENGINE_TCGEN05) choose_tile(M, N, kblocks, ctas, block_n);
+  else choose_tile_ts(M, N, kblocks, ctas, block_n);
   return QUIK_OK;
 }
 
@@ -226,19 +230,23 @@ int quik_unpack_int4(const uint8_t *src, int8_t *dst, int rows, int cols, void *
   return launch_unpack_int4(src, dst, rows, cols, static_cast<cudaStream_t>(stream));
 }
 
-static int widen_operands(const uint8_t *A, const uint8_t *B, int M, int N, int K, void *scratch,
-                          size_t scratch_bytes, cudaStream_t st, const int8_t **A8, const int8_t **B8) {
+// Brings packed int4 operands into the form the selected engine takes: the engine with the token operand in tensor
+// memory reads A packed and widens it on chip, so only B is widened into scratch; the others need both one per byte.
+// Returns the engine call's status.
+static int run_int4_gemm(const uint8_t *A, const uint8_t *B, int M, int N, int K, void *scratch, size_t scratch_bytes,
+                         const Epilogue &ep, cudaStream_t st) {
   if (!scratch || scratch_bytes < quik_int4_matmul_scratch_bytes(M, N, K)) return QUIK_ERR_SCRATCH;
   if ((reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) return QUIK_ERR_ALIGN;
   int8_t *a8 = static_cast<int8_t *>(scratch);
   int8_t *b8 = a8 + align256((size_t)M * K);
-  int rc = launch_unpack_int4(A, a8, M, K, st);
+  const int engine = g_engine.load();
+  const bool on_chip = (engine == QUIK_ENGINE_AUTO || engine == QUIK_ENGINE_TCGEN05_TS) && aligned16(A);
+  int rc = launch_unpack_int4(B, b8, N, K, st);
   if (rc != QUIK_OK) return rc;
-  rc = launch_unpack_int4(B, b8, N, K, st);
+  if (on_chip) return launch_gemm_tcgen05_ts(A, 1, b8, M, N, K, ep, st);
+  rc = launch_unpack_int4(A, a8, M, K, st);
   if (rc != QUIK_OK) return rc;
-  *A8 = a8;
-  *B8 = b8;
-  return QUIK_OK;
+  return run_int8_gemm(a8, b8, M, N, K, ep, st);
 }
 
 int quik_int4_matmul(const uint8_t *A, const uint8_t *B, int32_t *C, int M, int N, int K, void *scratch,
@@ -247,13 +255,10 @@ int quik_int4_matmul(const uint8_t *A, const uint8_t *B, int32_t *C, int M, int 
   if (M == 0 || N == 0) return QUIK_OK;
   if (!A || !B || !C) return QUIK_ERR_NULL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int8_t *a8, *b8;
-  int rc = widen_operands(A, B, M, N, K, scratch, scratch_bytes, st, &a8, &b8);
-  if (rc != QUIK_OK) return rc;
   Epilogue ep{};
   ep.mode = 0;
   ep.C = C;
-  return run_int8_gemm(a8, b8, M, N, K, ep, st);
+  return run_int4_gemm(A, B, M, N, K, scratch, scratch_bytes, ep, st);
 }
 
 int quik_fused_dequantize(const void *A, const void *B, int bits, const void *scale_row, const void *scale_col,
@@ -265,14 +270,7 @@ int quik_fused_dequantize(const void *A, const void *B, int bits, const void *sc
   if (!A || !B || !scale_row || !scale_col || !y || !out) return QUIK_ERR_NULL;
   if ((zero_row == nullptr) != (w_reduced == nullptr)) return QUIK_ERR_NULL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int8_t *a8 = static_cast<const int8_t *>(A), *b8 = static_cast<const int8_t *>(B);
-  if (bits == 4) {
-    int rc = widen_operands(static_cast<const uint8_t *>(A), static_cast<const uint8_t *>(B), M, N, K, scratch,
-                            scratch_bytes, st, &a8, &b8);
-    if (rc != QUIK_OK) return rc;
-  } else if (!aligned16(A) || !aligned16(B)) {
-    return QUIK_ERR_ALIGN;
-  }
+  if (bits == 8 && (!aligned16(A) || !aligned16(B))) return QUIK_ERR_ALIGN;
   Epilogue ep{};
   ep.mode = 1;
   ep.dtype = QUIK_F16;
@@ -283,7 +281,10 @@ int quik_fused_dequantize(const void *A, const void *B, int bits, const void *sc
   ep.w_reduced = w_reduced;
   ep.y = y;
   ep.shift_value = shift_value;
-  return run_int8_gemm(a8, b8, M, N, K, ep, st);
+  if (bits == 4)
+    return run_int4_gemm(static_cast<const uint8_t *>(A), static_cast<const uint8_t *>(B), M, N, K, scratch, scratch_bytes,
+                         ep, st);
+  return run_int8_gemm(static_cast<const int8_t *>(A), static_cast<const int8_t *>(B), M, N, K, ep, st);
 }
 
 int quik_mixed_linear(const void *q, int q_packed, const void *w, int w_packed, const void *meta,
@@ -320,9 +321,15 @@ int quik_mixed_linear_ld(const void *q, int q_packed, const void *w, int w_packe
   ep.fp_a = F > 0 ? fp_x : nullptr;
   ep.fp_b = F > 0 ? fp_w : nullptr;
   ep.F = F;
-  if (bits == 4 && (q_packed || w_packed)) {
+  if (bits == 4 && q_packed && !w_packed) {
+    // packed token codes against weights one per byte: tensor-core GEMM that widens the tokens on chip
+    const int engine = g_engine.load();
+    if (engine != QUIK_ENGINE_AUTO && engine != QUIK_ENGINE_TCGEN05_TS) return QUIK_ERR_UNSUPPORTED;
+    if (K_int % 32 != 0) return QUIK_ERR_SHAPE;
+    return launch_gemm_tcgen05_ts(q, 1, static_cast<const int8_t *>(w), M, N, K_int, ep, st);
+  }
+  if (bits == 4 && w_packed) {
     // packed int4 weights: weight-streaming engines (few tokens only)
-    if (!w_packed) return QUIK_ERR_UNSUPPORTED;
     if (K_int % 32 != 0) return QUIK_ERR_SHAPE;
     if (q_packed) {
       // mma.sync engines, both operands packed.  Automatic mode: layers of >= 16 MiB of packed weights go
@@ -397,14 +404,11 @@ int quik_int4_matmul_fixed_scratch(const uint8_t *A, const uint8_t *B, int32_t *
   int rc = fixed_scratch_for_current_device(&scratch);
   if (rc != QUIK_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int8_t *a8, *b8;
-  // both widened operands are rewritten in full by every call, so nothing has to be cleared first
-  rc = widen_operands(A, B, M, N, K, scratch, QUIK_NOALLOC_SCRATCH_BYTES, st, &a8, &b8);
-  if (rc != QUIK_OK) return rc;
+  // the part of the array that a call uses is rewritten in full by that call, so nothing has to be cleared first
   Epilogue ep{};
   ep.mode = 0;
   ep.C = C;
-  return run_int8_gemm(a8, b8, M, N, K, ep, st);
+  return run_int4_gemm(A, B, M, N, K, scratch, QUIK_NOALLOC_SCRATCH_BYTES, ep, st);
 }
 
 }  // extern "C"

@@ -191,6 +191,11 @@ int launch_gemm_tcgen05(const int8_t *A, const int8_t *B, int M, int N, int K, c
                         cudaStream_t st);
 int launch_gemm_mma_sync(const int8_t *A, const int8_t *B, int M, int N, int K, const Epilogue &ep,
                          cudaStream_t st);
+// tcgen05 GEMM with the A operand in tensor memory (gemm_tcgen05_ts.cu): A int8 [M, K], or packed int4 [M, K/2]
+// widened on chip when a_packed != 0 (K counts codes); B int8 [N, K]
+int launch_gemm_tcgen05_ts(const void *A, int a_packed, const int8_t *B, int M, int N, int K, const Epilogue &ep,
+                           cudaStream_t st);
+void choose_tile_ts(int M, int N, int kblocks, int *ctas_out, int *bn_out);
 int launch_small_m(const void *q, const void *w, int bits, int M, int N, int K_int,
                    const Epilogue &ep, cudaStream_t st);
 // TMA-fed mma.sync weight streaming (stream_w_mma.cu): q and w in the reference's storage format

@@ -30,6 +30,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "gemm_epilogue.cuh"
 #include "tcgen05_ptx.cuh"
 
 namespace quik {
@@ -38,10 +39,7 @@ __device__ unsigned int g_device_status = 0;
 
 namespace {
 
-constexpr int BLOCK_M = 128;
-constexpr int STAGE_K_BYTES = 128;           // one 128B-swizzle row of K per stage
 constexpr int NUM_THREADS = 320;              // TMA warp + MMA warp + 8 epilogue warps
-constexpr int NUM_EPI_THREADS = 256;
 // Process-wide tuning knobs (quik_config_set): plain words, meant to be set once before the layers run; a
 // launch reads each of them once.
 std::atomic<int> g_tile_n{0};                                 // 0 = choose by shape, else a multiple of 16 in [32, 256]
@@ -51,76 +49,14 @@ std::atomic<unsigned long long *> g_dbg{nullptr};             // diagnostic coun
 // Shared-memory plan after the 1024-byte aligned ring of stages: 256 bytes of barriers etc. and the
 // per-warp epilogue vectors (rounded to 1024 together), then one output staging chunk per epilogue
 // warp (32 rows x 64 bytes).
-constexpr int EPI_BUF_BYTES = 32 * 64;
 constexpr int AUX_BYTES(int cap_n) { return ((256 + 8 * 3 * (cap_n / 2) * 4) + 1023) / 1024 * 1024; }
 constexpr int stage_bytes(int cap_n, int ctas) { return (BLOCK_M + cap_n / ctas) * STAGE_K_BYTES; }
-constexpr int SMEM_LIMIT = 227 * 1024;
 // Ring depth: as many stages as fit (at most 8).
 constexpr int num_stages(int cap_n, int ctas) {
   const int n = (SMEM_LIMIT - 1024 - AUX_BYTES(cap_n) - 8 * EPI_BUF_BYTES) / stage_bytes(cap_n, ctas);
   return n > 8 ? 8 : n;
 }
 
-struct GemmParams {
-  int M, N;
-  int block_n;                    // tile width: multiple of 16, <= CAP_N
-  int split_n;                    // columns of a tile that the first four epilogue warps take (multiple of 32 or block_n)
-  int num_m_tiles, num_tiles;
-  int int_kb, fp_kb;              // k-blocks per tile: integer (128 B each) and outlier (64 elems)
-  uint32_t idesc_int, idesc_fp;   // tcgen05 instruction descriptors
-  int mode;                       // 0: int32 C, 1: dequantize
-  int32_t *C;
-  void *out;
-  long long ldo;                  // row pitch of `out` in elements (>= N)
-  const void *row_scale;          // element (row * row_stride)
-  const void *row_zero;           // may be NULL
-  int row_stride;
-  const void *scale_col, *w_reduced, *bias, *y;
-  float shift_value;
-  int vec_out;                    // 16-byte stores allowed (pitch and base aligned)
-  int vec_y;
-  unsigned long long *dbg;         // optional per-CTA cycle counters (16 per CTA), NULL = off
-};
-
-// mbarrier / TMA / TMEM / tcgen05 wrappers: tcgen05_ptx.cuh
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-  return mbar_wait(bar, parity, abort_flag, &g_device_status);
-}
-
-template <typename T> __device__ __forceinline__ float ldf(const void *p, size_t i) {
-  return Traits<T>::to_float(static_cast<const T *>(p)[i]);
-}
-
-// 32 consecutive values of type T: 16-byte vector access when `vec`, scalar with a column guard
-// otherwise.
-template <typename T>
-__device__ __forceinline__ void load_row32(const T *src, bool vec, int ncols_left, T (&v)[32]) {
-  if (vec) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) reinterpret_cast<uint4 *>(v)[j] = reinterpret_cast<const uint4 *>(src)[j];
-  } else {
-    for (int j = 0; j < 32; ++j) v[j] = (j < ncols_left) ? src[j] : Traits<T>::from_float(0.f);
-  }
-}
-// eight fp32 values -> eight values of type T in one 16-byte word
-template <typename T>
-__device__ __forceinline__ uint4 pack8(const float *o) {
-  uint4 pk;
-  T *pe = reinterpret_cast<T *>(&pk);
-#pragma unroll
-  for (int e = 0; e < 8; ++e) pe[e] = Traits<T>::from_float(o[e]);
-  return pk;
-}
-template <typename T>
-__device__ __forceinline__ void store_row32(T *dst, bool vec, int ncols_left, const float (&o)[32]) {
-  if (vec) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) reinterpret_cast<uint4 *>(dst)[j] = pack8<T>(o + 8 * j);
-  } else {
-    for (int j = 0; j < 32; ++j)
-      if (j < ncols_left) dst[j] = Traits<T>::from_float(o[j]);
-  }
-}
 // ---------------------------------------------------------------------------------------------
 // Work of one CTA = its tiles t_0, t_1, ... (tile index blockIdx.x + j * gridDim.x).  TMEM holds
 // two accumulator regions (CAP_N columns apart); tile j uses region j & 1 for BOTH of its products,
@@ -223,7 +159,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int m0 = (tile % p.num_m_tiles) * TILE_M + rank * BLOCK_M;      // this CTA's rows of A
         const int n0 = (tile / p.num_m_tiles) * bn + rank * b_rows;           // this CTA's rows of B
         for (int kb = kb0; kb < kb1 && ok; ++kb) {
-          if (!mbar_wait(smem_u32(empty_bar + stage), phase ^ 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(empty_bar + stage), phase ^ 1, abort_flag, p.status)) { ok = false; break; }
           const uint32_t fb = smem_u32(full_bar + stage);
           const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
           if (rank == 0) mbar_expect_tx(fb, stage_tx);
@@ -263,12 +199,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const bool after_drain = HAS_FP && !fp;
             const uint32_t bar = smem_u32((after_drain ? fp_drained : acc_empty) + r);
             const long long t0 = clock64();
-            if (!mbar_wait(bar, after_drain ? use_parity : (use_parity ^ 1u), abort_flag)) { ok = false; break; }
+            if (!mbar_wait(bar, after_drain ? use_parity : (use_parity ^ 1u), abort_flag, p.status)) { ok = false; break; }
             w_region += clock64() - t0;
             tc_fence_after();
           }
           const long long t1 = clock64();
-          if (!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag, p.status)) { ok = false; break; }
           w_full += clock64() - t1;
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
@@ -301,238 +237,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
   } else {
-    // ================= epilogue (warps 2..9) =================
-    // Warp (sub, half) owns rows [32*sub, 32*sub+32) of the tile and the columns [cb, cb + cn): the first
-    // split_n columns for half 0, the rest for half 1.  It walks them 32 at a time; the last step of a range
-    // whose length is not a multiple of 32 holds 16 valid columns (`valid` below), the rest is ignored.
-    const int e = warp - 2;
-    const int sub = warp & 3;                 // TMEM lane quarter this warp may read
-    const int half = e >> 2;                  // which part of the tile's columns
-    const int cb = half ? p.split_n : 0;
-    const int cn = half ? bn - p.split_n : p.split_n;
-    const int cn32 = (cn + 31) & ~31;
-    float *s_scol = s_vec + e * 3 * HALF_CAP;
-    float *s_wred = s_scol + HALF_CAP;
-    float *s_bias = s_wred + HALF_CAP;
-    unsigned char *s_stage = s_out + e * EPI_BUF_BYTES;   // staging of one 32 x 32 output chunk
-    bool ok = true;
-    long long e_wait_fp = 0, e_wait_acc = 0, e_drain = 0, e_finish = 0;
-
-    // Where the outlier product of (this warp, tile) is parked inside the tile's place in `out`.
-    // Every full 32 x 32 chunk is parked inside its own 32-row x 64-byte block (so the final store of one
-    // chunk never touches the parked data of another), but permuted: the jj-th 16-byte piece of lane
-    // L goes to row 8*jj + L/4, piece L%4 of the block, so one warp instruction writes 8 rows x 64
-    // contiguous bytes (whole sectors) instead of 32 rows x 16 bytes.  The same lane reads its pieces
-    // back from the same addresses; nobody else looks at them.  Chunks that touch the matrix edge or hold
-    // fewer than 32 valid columns keep the plain row-per-lane layout with guards.
-    auto parked_piece = [&](T *sub_base, int c0, int jj) -> uint4 * {   // sub_base = &out[first row of warp][n0]
-      return reinterpret_cast<uint4 *>(sub_base + (size_t)(8 * jj + (lane >> 2)) * p.ldo + c0) + (lane & 3);
-    };
-
-    // park T(outlier product + bias) of tile j in `out`
-    auto drain = [&](int j) {
-      const int tile = unit + j * num_units;
-      const int m0 = (tile % p.num_m_tiles) * TILE_M + rank * BLOCK_M + sub * 32;   // first row of this warp
-      const int n0 = (tile / p.num_m_tiles) * bn + cb;
-      const int lim = min(p.N - n0, cn);       // valid columns from n0 on (<= 0: none)
-      const int r = j & 1;
-      __syncwarp();
-      for (int c = lane; c < cn32; c += 32)
-        s_bias[c] = (c < lim && p.bias) ? ldf<T>(p.bias, n0 + c) : 0.f;
-      __syncwarp();
-      const long long tw = clock64();
-      const bool ready = mbar_wait(smem_u32(fp_full + r), (uint32_t)(j >> 1) & 1u, abort_flag);
-      if (!__all_sync(0xffffffffu, ready)) { ok = false; return; }
-      const long long tw1 = clock64();
-      e_wait_fp += tw1 - tw;
-      tc_fence_after();
-      const int row = m0 + lane;
-      const bool rows_in = m0 + 32 <= p.M;
-      T *sub_base = static_cast<T *>(p.out) + (size_t)m0 * p.ldo + n0;
-      const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + r * CAP_N + cb;
-#pragma unroll 1
-      for (int c0 = 0; c0 < cn; c0 += 32) {
-        uint32_t f[32];
-        float o[32];
-        __syncwarp();                          // tcgen05.ld is warp-collective
-        tmem_ld32(taddr + c0, f);
-        tmem_ld_wait();
-        const int valid = lim - c0;            // warp-uniform
-        if (valid <= 0) continue;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(f[i]) + s_bias[c0 + i];
-        if (p.vec_out && rows_in && valid >= 32) {
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj) *parked_piece(sub_base, c0, jj) = pack8<T>(o + 8 * jj);
-        } else if (row < p.M) {
-          T *dst = static_cast<T *>(p.out) + (size_t)row * p.ldo + n0 + c0;
-          if (p.vec_out) {                     // valid is a multiple of 8 here
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj)
-              if (8 * jj < valid) reinterpret_cast<uint4 *>(dst)[jj] = pack8<T>(o + 8 * jj);
-          } else {
-            store_row32<T>(dst, false, valid, o);
-          }
-        }
-      }
-      tc_fence_before();
-      if (CTAS == 1) mbar_arrive(smem_u32(fp_drained + r));
-      else mbar_arrive_leader(smem_u32(fp_drained + r));
-      e_drain += clock64() - tw1;
-    };
-
-    auto finish = [&](int j) {
-      const int tile = unit + j * num_units;
-      const int m0 = (tile % p.num_m_tiles) * TILE_M + rank * BLOCK_M + sub * 32;   // first row of this warp
-      const int n0 = (tile / p.num_m_tiles) * bn + cb;
-      const int lim = min(p.N - n0, cn);
-      const int r = j & 1;
-      if (p.mode == 1) {
-        __syncwarp();                         // previous readers of the vectors are done
-        for (int c = lane; c < cn32; c += 32) {
-          const int col = n0 + c;
-          const bool in = c < lim;
-          s_scol[c] = in ? ldf<T>(p.scale_col, col) : 0.f;
-          s_wred[c] = (in && p.w_reduced) ? ldf<T>(p.w_reduced, col) : 0.f;
-          s_bias[c] = (in && p.bias && !HAS_FP) ? ldf<T>(p.bias, col) : 0.f;   // with outliers the drain added it
-        }
-        __syncwarp();
-      }
-      const int row = m0 + lane;
-      const bool row_ok = row < p.M;
-      const bool rows_in = m0 + 32 <= p.M;
-      T *sub_base = static_cast<T *>(p.out) + (size_t)m0 * p.ldo + n0;
-      const T *my_row = static_cast<const T *>(p.out) + (size_t)row * p.ldo + n0;
-      // The parked outlier product of the first 32 columns is fetched before waiting for the integer
-      // product, the following ones one step ahead, so their L2 latency stays off the critical path.
-      uint4 pk_next[4];
-      auto prefetch_parked = [&](int c0) {
-        if (!HAS_FP || p.mode != 1 || !p.vec_out) return;
-        const int valid = lim - c0;
-        if (rows_in && valid >= 32) {
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj) pk_next[jj] = *parked_piece(sub_base, c0, jj);
-        } else if (row_ok) {
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj)
-            if (8 * jj < valid) pk_next[jj] = reinterpret_cast<const uint4 *>(my_row + c0)[jj];
-        }
-      };
-      prefetch_parked(0);
-      const long long tw = clock64();
-      const bool ready = mbar_wait(smem_u32(acc_full + r), (uint32_t)(j >> 1) & 1u, abort_flag);
-      if (!__all_sync(0xffffffffu, ready)) { ok = false; return; }
-      const long long tw1 = clock64();
-      e_wait_acc += tw1 - tw;
-      tc_fence_after();
-      float srow = 0.f, zs = 0.f;
-      if (p.mode == 1 && row_ok) {
-        srow = ldf<T>(p.row_scale, (size_t)row * p.row_stride);
-        const float zrow = p.row_zero ? ldf<T>(p.row_zero, (size_t)row * p.row_stride) : 0.f;
-        zs = fmaf(p.shift_value, srow, zrow);
-      }
-      const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + r * CAP_N + cb;
-#pragma unroll 1
-      for (int c0 = 0; c0 < cn; c0 += 32) {
-        uint32_t v[32];
-        uint4 pk[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) pk[i] = pk_next[i];
-        __syncwarp();                          // tcgen05.ld is warp-collective: reconverge first
-        tmem_ld32(taddr + c0, v);
-        if (c0 + 32 < cn) prefetch_parked(c0 + 32);
-        tmem_ld_wait();
-        const int valid = lim - c0;            // warp-uniform
-        if (valid <= 0) continue;
-        const int col0 = n0 + c0;
-        const size_t off = (size_t)row * p.N + col0;
-        if (p.mode == 0) {
-          if (!row_ok) continue;
-          if (p.vec_out) {                     // valid is a multiple of 4 here
-            int4 *dst = reinterpret_cast<int4 *>(p.C + off);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (4 * i < valid) dst[i] = make_int4((int)v[4 * i], (int)v[4 * i + 1], (int)v[4 * i + 2], (int)v[4 * i + 3]);
-          } else {
-            for (int i = 0; i < 32; ++i)
-              if (i < valid) p.C[off + i] = (int)v[i];
-          }
-          continue;
-        }
-        float o[32];   // addend first, result later
-        if (HAS_FP) {
-          if (p.vec_out) {
-            const T *pe = reinterpret_cast<const T *>(pk);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = Traits<T>::to_float(pe[i]);   // pieces beyond `valid` are never stored
-          } else {
-            for (int i = 0; i < 32; ++i)
-              o[i] = (row_ok && i < valid) ? Traits<T>::to_float(my_row[c0 + i]) : 0.f;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = s_bias[c0 + i];
-        }
-        if (p.y != nullptr && row_ok) {
-          T yv[32];
-          load_row32<T>(static_cast<const T *>(p.y) + off, valid >= 32 && p.vec_y, valid, yv);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] += Traits<T>::to_float(yv[i]);
-        }
-#pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
-          const float4 sc4 = reinterpret_cast<const float4 *>(s_scol + c0)[i4];
-          const float4 wr4 = reinterpret_cast<const float4 *>(s_wred + c0)[i4];
-          const float sc[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
-          const float wr[4] = {wr4.x, wr4.y, wr4.z, wr4.w};
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int i = 4 * i4 + q;
-            // out = acc * (s_row * s_col) + ((zero + shift * s_row) * w_red + addend), fused multiply-adds
-            o[i] = fmaf((float)(int)v[i], srow * sc[q], fmaf(zs, wr[q], o[i]));
-          }
-        }
-        if (p.vec_out) {
-          // Transpose through shared memory so that one warp instruction stores 8 rows x 64 contiguous
-          // bytes (whole sectors) instead of 32 rows x 16 bytes: lane i writes its row as four 16-byte
-          // pieces (swizzled against bank conflicts), lane L then stores piece L%4 of rows 8k + L/4.
-          __syncwarp();                        // the previous chunk has been read out of the buffer
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj)
-            *reinterpret_cast<uint4 *>(s_stage + lane * 64 + ((jj ^ ((lane >> 1) & 3)) << 4)) = pack8<T>(o + 8 * jj);
-          __syncwarp();
-          const int pc = lane & 3;
-          const bool col_ok = 8 * pc + 8 <= valid;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int rr = 8 * k + (lane >> 2);
-            const uint4 piece = *reinterpret_cast<const uint4 *>(s_stage + rr * 64 + ((pc ^ ((rr >> 1) & 3)) << 4));
-            if (col_ok && m0 + rr < p.M)
-              *(reinterpret_cast<uint4 *>(static_cast<T *>(p.out) + (size_t)(m0 + rr) * p.ldo + col0) + pc) = piece;
-          }
-        } else if (row_ok) {
-          store_row32<T>(static_cast<T *>(p.out) + (size_t)row * p.ldo + col0, false, valid, o);
-        }
-      }
-      tc_fence_before();
-      if (CTAS == 1) mbar_arrive(smem_u32(acc_empty + r));
-      else mbar_arrive_leader(smem_u32(acc_empty + r));
-      e_finish += clock64() - tw1;
-    };
-
-    if (HAS_FP && n_local > 0) drain(0);
-    for (int j = 0; j < n_local && ok; ++j) {
-      if (HAS_FP && j + 1 < n_local) drain(j + 1);
-      if (!ok) break;
-      finish(j);
-    }
-    if (p.dbg && warp == 2 && lane == 0) {
-      unsigned long long *d = p.dbg + (size_t)blockIdx.x * 16;
-      d[4] = (unsigned long long)e_wait_fp;     // epilogue warp: waiting for an outlier product
-      d[5] = (unsigned long long)e_wait_acc;    // ... waiting for an integer product
-      d[6] = (unsigned long long)e_drain;       // ... parking outlier products
-      d[7] = (unsigned long long)e_finish;      // ... final epilogues
-    }
+    // ================= epilogue (warps 2..9): gemm_epilogue.cuh =================
+    EpilogueWarp<T, HAS_FP, CTAS> ew(p, tmem_base, CAP_N, unit, num_units, rank, warp - 2, warp & 3, lane, s_vec,
+                                     HALF_CAP, s_out, acc_full, acc_empty, fp_full, fp_drained, abort_flag);
+    ew.run(n_local);
+    if (p.dbg && warp == 2 && lane == 0) ew.write_counters((int)blockIdx.x);
   }
 
   // ---- teardown: every thread arrives here, also after an aborted wait
@@ -762,37 +471,15 @@ int launch_gemm_tcgen05(const int8_t *A, const int8_t *B, int M, int N, int K, c
   const int m_tiles = (M + tile_m - 1) / tile_m;
   const int cap_n = block_n <= 128 ? 128 : 256;
 
-  p.M = M;
-  p.N = N;
+  fill_epilogue_params(p, ep, M, N);
+  if (p.status == nullptr) return QUIK_ERR_CUDA;
   p.block_n = block_n;
-  p.split_n = ((block_n / 2 + 31) & ~31) < block_n ? ((block_n / 2 + 31) & ~31) : block_n;
+  p.split_n = split_columns(block_n);
   p.num_m_tiles = m_tiles;
   p.num_tiles = m_tiles * ((N + block_n - 1) / block_n);
   p.idesc_int = make_idesc(2, 1, tile_m, block_n);                              // S32 accumulate, signed 8-bit operands
   p.idesc_fp = make_idesc(1, ep.dtype == QUIK_BF16 ? 1 : 0, tile_m, block_n);   // F32 accumulate, F16 / BF16 operands
-  p.mode = ep.mode;
-  p.C = ep.C;
-  p.out = ep.out;
-  p.ldo = ep.ldo > 0 ? ep.ldo : N;
-  if (ep.meta) {
-    const size_t eb = 2;
-    p.row_scale = ep.meta;
-    p.row_zero = static_cast<const unsigned char *>(ep.meta) + eb;
-    p.row_stride = 2;
-  } else {
-    p.row_scale = ep.scale_row;
-    p.row_zero = ep.zero_row;
-    p.row_stride = 1;
-  }
-  p.scale_col = ep.scale_col;
-  p.w_reduced = ep.w_reduced;
-  p.bias = ep.bias;
-  p.y = ep.y;
-  p.shift_value = ep.shift_value;
-  if (ep.mode == 0) p.vec_out = (N % 4 == 0) && aligned16(ep.C);
-  else p.vec_out = (N % 8 == 0) && (p.ldo % 8 == 0) && aligned16(ep.out);
-  p.vec_y = ep.y && (N % 8 == 0) && aligned16(ep.y);
-  p.dbg = g_dbg.load();
+  p.acc_shift = 0;
 
   CUtensorMap ta, tb, tfa, tfb;
   int rc;

@@ -72,39 +72,6 @@ struct StreamParams {
   unsigned long long *dbg;        // optional cycle counters (16 per CTA), NULL = off
 };
 
-__device__ __forceinline__ void mma_i8_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}"
-               ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
-        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
-        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-               : "r"(taddr)
-               : "memory");
-}
-
-// Eight packed int4 codes (k0 in the lowest nibble) -> two words of signed bytes in k order, each byte
-// = 16 * code: a nibble moved to the high half of its byte is the code times 16 in two's complement.
-__device__ __forceinline__ void widen8(uint32_t w, uint32_t &k0123, uint32_t &k4567) {
-  const uint32_t even = (w << 4) & 0xF0F0F0F0u;   // codes k0 k2 k4 k6
-  const uint32_t odd = w & 0xF0F0F0F0u;           // codes k1 k3 k5 k7
-  k0123 = __byte_perm(even, odd, 0x5140);
-  k4567 = __byte_perm(even, odd, 0x7362);
-}
-
 template <typename T, int BITS, int NTOK>
 __global__ void __launch_bounds__(SW_THREADS, SwCfg<NTOK>::CTAS_PER_SM)
 stream_w_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
@@ -292,7 +259,7 @@ stream_w_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
 #pragma unroll
           for (int kk = 0; kk < 8 / SW_ISSUERS; ++kk) {      // 32 codes = 8 TMEM columns of A per instruction
             const int k = kk * SW_ISSUERS + issuer;
-            mma_i8_ts(tmem_base + SW_D_INT + SW_TOKENS * issuer, a + 8 * k, (k < 4 ? dx : dx1) + 2 * (k & 3), p.idesc_int,
+            mma_i8_ts<1>(tmem_base + SW_D_INT + SW_TOKENS * issuer, a + 8 * k, (k < 4 ? dx : dx1) + 2 * (k & 3), p.idesc_int,
                       (ii > 0 || kk > 0) ? 1u : 0u);
           }
           mma_commit<1>(smem_u32(a_empty + slot));

@@ -160,22 +160,35 @@ class MixedQLinear(torch.nn.Module):
             return self._forward_unfused(x, shared_input)
 
         M = x.shape[0]
-        # Above SMALL_M_MAX tokens: tensor-core GEMM on codes widened to one per byte (both operands).  Below:
-        # weight streaming, the weights stay packed; the tcgen05 engine takes the token codes one per byte, the
-        # mma.sync engine (the default for 4-bit layers: faster on the layer sizes measured) packed like the weights.
-        # From 17 to STREAM_M_MAX tokens only the tcgen05 streaming engine applies.
-        # (a packed 4-bit row must be a multiple of 16 bytes for the streaming engines; otherwise the tiled GEMM)
-        stream = M <= _lib.STREAM_M_MAX and _lib.small_m_mode != _lib.SMALL_M_OFF \
-            and (self.bits == 8 or self.int_features_num % 32 == 0)
-        wide = not (stream and M <= _lib.SMALL_M_MAX and _lib.small_m_mode != _lib.SMALL_M_TCGEN05)
+        # Operand layouts by engine (the C side picks the engine from them, include/quik_b200.h):
+        #   up to STREAM_M_MAX tokens: weight streaming, the weights stay in their storage format; the tcgen05
+        #     streaming engine takes the token codes one per byte, the mma.sync engines (up to SMALL_M_MAX tokens, the
+        #     default for 4-bit layers) packed like the weights;
+        #   more tokens: tensor-core GEMM on weight codes one per byte; 4-bit token codes stay packed (the reference
+        #     layout) and are widened on chip when the engine with the token operand in tensor memory is selected,
+        #     else the quantizer writes them one per byte.
+        # (a packed 4-bit row must be a multiple of 16 bytes for these engines; otherwise both operands one per byte)
+        small_m_mode = _lib.config_get(_lib.CFG_SMALL_M)
+        row_ok = self.bits == 8 or self.int_features_num % 32 == 0
+        stream = M <= _lib.STREAM_M_MAX and small_m_mode != _lib.SMALL_M_OFF and row_ok
+        if self.bits == 8:
+            q_packed = w_packed = False
+        elif stream:
+            q_packed = M <= _lib.SMALL_M_MAX and small_m_mode != _lib.SMALL_M_TCGEN05
+            w_packed = True
+        else:
+            q_packed = row_ok and _lib.config_get(_lib.CFG_GEMM_ENGINE) in (_lib.ENGINE_AUTO, _lib.ENGINE_TCGEN05_TS)
+            w_packed = False
+        wide = not q_packed
+        if shared_input.qint_x is not None and self.bits == 4 and shared_input.wide != wide:
+            raise RuntimeError("MixedQLinear: the shared quantized input was written in another code layout than this "
+                               "member needs (the members of a group must run on the same engine)")
         if shared_input.qint_x is None:
             i16, f16 = self._idx16()
             shared_input.qint_x, shared_input.meta, shared_input.fp_x = asymmetric.quantize_u16(
                 x, i16, f16, self.bits, wide)
             shared_input.wide = wide
         q = shared_input.qint_x
-        q_packed = self.bits == 4 and not shared_input.wide
-        w_packed = self.bits == 4 and (stream or q_packed)
         w = self.int_weight if (w_packed or self.bits == 8) else self._weight_codes_int8()
         N = self.out_features
         hook = MixedQLinear.launch_hook
@@ -202,6 +215,10 @@ class MixedQLinear(torch.nn.Module):
 
     def _forward_unfused(self, x, shared_input):
         """The reference's operator sequence (experiments/qlinear.py:105-148)."""
+        group_input = shared_input
+        if shared_input.qint_x is not None and self.bits == 4 and shared_input.wide:
+            # a fused member of the group left its codes one per byte; the reference operators take the packed layout
+            shared_input = SharedQuantizedInput(1)
         if shared_input.qint_x is None:
             shared_input.qint_x, shared_input.meta, shared_input.fp_x = asymmetric.quantize(
                 x, self.int_indices, self.fp_indices, self.bits)
@@ -219,6 +236,8 @@ class MixedQLinear(torch.nn.Module):
         output = asymmetric.dequantize(int_result, shared_input.meta, self.weights_scales, self.reduced_w,
                                        fp_result, self.bits)
         shared_input.finish()
+        if group_input is not shared_input:
+            group_input.finish()
         return output.reshape((1, *output.shape))
 
     def _forward_symmetric(self, x, shared_input):

@@ -9,7 +9,7 @@ from tests.gpu_util import assert_device_clean, dev
 pytestmark = pytest.mark.gpu
 
 # (id, engine, tile width, CTA-pair mode: 1 = single CTAs, 2 = CTA pairs)
-ENGINES = [("mma_sync", _lib.ENGINE_MMA_SYNC, 0, 0), ("tcgen05_auto", _lib.ENGINE_TCGEN05, 0, 0),
+ENGINES = [("mma_sync", _lib.ENGINE_MMA_SYNC, 0, 0), ("auto", _lib.ENGINE_AUTO, 0, 0), ("tcgen05_auto", _lib.ENGINE_TCGEN05, 0, 0),
            ("tcgen05_1cta_n128", _lib.ENGINE_TCGEN05, 128, 1), ("tcgen05_1cta_n256", _lib.ENGINE_TCGEN05, 256, 1),
            ("tcgen05_pair_n128", _lib.ENGINE_TCGEN05, 128, 2), ("tcgen05_pair_n256", _lib.ENGINE_TCGEN05, 256, 2),
            # tile widths that are not a power of two (chosen per problem against partial waves); 240, 208, 176,
@@ -17,7 +17,12 @@ ENGINES = [("mma_sync", _lib.ENGINE_MMA_SYNC, 0, 0), ("tcgen05_auto", _lib.ENGIN
            ("tcgen05_pair_n240", _lib.ENGINE_TCGEN05, 240, 2), ("tcgen05_pair_n224", _lib.ENGINE_TCGEN05, 224, 2),
            ("tcgen05_pair_n208", _lib.ENGINE_TCGEN05, 208, 2), ("tcgen05_1cta_n176", _lib.ENGINE_TCGEN05, 176, 1),
            ("tcgen05_pair_n144", _lib.ENGINE_TCGEN05, 144, 2), ("tcgen05_1cta_n96", _lib.ENGINE_TCGEN05, 96, 1),
-           ("tcgen05_pair_n48", _lib.ENGINE_TCGEN05, 48, 2)]
+           ("tcgen05_pair_n48", _lib.ENGINE_TCGEN05, 48, 2),
+           # the engine that moves the token operand into tensor memory (4-bit codes widened on chip): widths up to 224
+           ("tcgen05_ts_auto", _lib.ENGINE_TCGEN05_TS, 0, 0), ("tcgen05_ts_pair_n224", _lib.ENGINE_TCGEN05_TS, 224, 2),
+           ("tcgen05_ts_pair_n208", _lib.ENGINE_TCGEN05_TS, 208, 2), ("tcgen05_ts_pair_n192", _lib.ENGINE_TCGEN05_TS, 192, 2),
+           ("tcgen05_ts_1cta_n224", _lib.ENGINE_TCGEN05_TS, 224, 1), ("tcgen05_ts_1cta_n144", _lib.ENGINE_TCGEN05_TS, 144, 1),
+           ("tcgen05_ts_pair_n128", _lib.ENGINE_TCGEN05_TS, 128, 2), ("tcgen05_ts_pair_n48", _lib.ENGINE_TCGEN05_TS, 48, 2)]
 
 
 @pytest.fixture(params=ENGINES, ids=[e[0] for e in ENGINES])

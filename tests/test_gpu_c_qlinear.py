@@ -51,10 +51,11 @@ def test_fused_forward_matches_oracle(dtype, M, K, N, F, bits):
 
 
 @pytest.mark.parametrize("col_pad", [8, 3])
+@pytest.mark.parametrize("engine", [_lib.ENGINE_TCGEN05, _lib.ENGINE_TCGEN05_TS], ids=["smem_operands", "tmem_operand"])
 @pytest.mark.parametrize("tile,pair", [(0, 0), (240, 2), (144, 2), (176, 1)])
 @pytest.mark.parametrize("M,K,N,F,bits", [(300, 1088, 520, 64, 4), (129, 1088, 264, 64, 8), (257, 608, 1000, 32, 4),
                                           (16, 1088, 520, 64, 4), (100, 1088, 520, 64, 8)])
-def test_fused_layer_writes_only_its_columns(M, K, N, F, bits, tile, pair, col_pad):
+def test_fused_layer_writes_only_its_columns(M, K, N, F, bits, tile, pair, engine, col_pad):
     """The layer's output is a window of a poisoned slab (rows and columns of padding on every side, handed over as
     `out_buffer` with a row pitch wider than N): the window equals the plain forward bit for bit and the padding is
     untouched.  col_pad = 8 keeps the window 16-byte aligned (vector stores, parked outlier products in the
@@ -65,6 +66,7 @@ def test_fused_layer_writes_only_its_columns(M, K, N, F, bits, tile, pair, col_p
     row_pad = 5
     poison = -1234.0
     try:
+        _lib.set_engine(engine)
         _lib.set_tile_n(tile)
         _lib.set_cta_pair(pair)
         want = case.module(case.x.unsqueeze(0))[0].clone()
@@ -76,6 +78,7 @@ def test_fused_layer_writes_only_its_columns(M, K, N, F, bits, tile, pair, col_p
         torch.cuda.synchronize()
     finally:
         case.module.out_buffer = None
+        _lib.set_engine(_lib.ENGINE_AUTO)
         _lib.set_tile_n(0)
         _lib.set_cta_pair(0)
     assert_device_clean()
@@ -143,6 +146,29 @@ def test_streaming_engine_up_to_128_tokens(dtype, M, K, N, F, bits):
     tol = TOL_RMS if dtype == torch.float16 else 4e-2
     assert rel_rms_err(out.cpu(), _oracle_out(case, round_y=False)) < tol
     assert rel_rms_err(out, tiled) < (5e-3 if dtype == torch.float16 else 4e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,N,F,bits", [(129, 1088, 520, 64, 4), (300, 4352, 1024, 256, 4), (2048, 4096, 1280, 256, 4),
+                                          (257, 11264, 520, 256, 8), (513, 1024, 264, 0, 4), (400, 2080, 96, 32, 8),
+                                          (1000, 4128, 4096, 32, 4)])
+def test_tensor_memory_operand_engine_matches_shared_memory_engine(dtype, M, K, N, F, bits):
+    """The two tcgen05 engines (token codes one per byte from shared memory; packed 4-bit codes widened on chip into
+    tensor memory) compute every output element from the same exact integer sum and the same order of outlier
+    products, so their results are identical bit for bit whatever tiles they pick; both match the oracle."""
+    case = make_layer("t", M, K, N, bits, F=F, seed=M + N, device=dev(), dtype=dtype, clip=False)
+    outs = {}
+    try:
+        for eng in (_lib.ENGINE_TCGEN05, _lib.ENGINE_TCGEN05_TS):
+            _lib.set_engine(eng)
+            outs[eng] = case.module(case.x.unsqueeze(0))[0].clone()
+            assert torch.equal(outs[eng], case.module(case.x.unsqueeze(0))[0])
+    finally:
+        _lib.set_engine(_lib.ENGINE_AUTO)
+    assert_device_clean()
+    assert torch.equal(outs[_lib.ENGINE_TCGEN05], outs[_lib.ENGINE_TCGEN05_TS])
+    tol = TOL_RMS if dtype == torch.float16 else 4e-2
+    assert rel_rms_err(outs[_lib.ENGINE_TCGEN05_TS].cpu(), _oracle_out(case, round_y=False)) < tol
 
 
 @pytest.mark.parametrize("M", [16, 300])
