@@ -41,10 +41,12 @@ extern "C" {
 
 /* ---- integer-GEMM engines (quik_config_set(QUIK_CFG_GEMM_ENGINE, ...)) -------------------- */
 #define QUIK_CFG_GEMM_ENGINE   1
-#define QUIK_ENGINE_AUTO       0    /* the fastest engine the shape allows (tcgen05 with the token operand in tensor memory) */
+#define QUIK_ENGINE_AUTO       0    /* the fastest engine measured: tcgen05 with both operands in shared memory         */
 #define QUIK_ENGINE_TCGEN05    1    /* tcgen05, both operands read from shared memory                              */
 #define QUIK_ENGINE_MMA_SYNC   2    /* legacy mma.sync tensor path (comparison engine)                            */
-#define QUIK_ENGINE_TCGEN05_TS 3    /* tcgen05, token operand moved (4-bit codes: widened) into tensor memory      */
+#define QUIK_ENGINE_TCGEN05_TS 3    /* tcgen05, token operand moved (4-bit codes: widened) into tensor memory; measured
+                                       slower (the small operand ring in tensor memory cannot hide the hand-over
+                                       latency), kept as the comparison engine for packed 4-bit operand loads     */
 /* Output-tile width of the tcgen05 engine: 0 = chosen per problem (so that the tiles fill whole waves of CTAs),
  * else a multiple of 16 from 32 to 256. */
 #define QUIK_CFG_TILE_N        2
@@ -61,6 +63,11 @@ extern "C" {
  * it waits for the predecessor's completion before its first global load or store, so results are those of
  * plain stream order; 0 launches in plain stream order. */
 #define QUIK_CFG_PDL           5
+/* Threads that issue the integer products of a tile in the tcgen05 engine with both operands in shared memory: 2
+ * (default) two threads share the k-slices of every block of a long sum (K_int >= 2048) and accumulate into the same
+ * tensor-memory accumulator -- one thread cannot issue these instructions as fast as the tensor pipe executes them;
+ * integer sums do not depend on the order of their terms; 1 a single thread issues everything. */
+#define QUIK_CFG_MMA_ISSUERS   6
 
 const char *quik_version(void);
 const char *quik_strerror(int status);
@@ -206,7 +213,7 @@ int quik_fused_dequantize(const void *A, const void *B, int bits,
  * 4-bit layers choose the engine by the operand layout:
  *   q one per byte, w one per byte   tensor-core GEMM (any M);
  *   q packed,       w one per byte   tensor-core GEMM whose token operand is widened on chip on its way into tensor
- *                                    memory (any M, K_int % 32 == 0; engine AUTO or TCGEN05_TS);
+ *                                    memory (any M, K_int % 32 == 0; engine TCGEN05_TS only);
  *   q one per byte, w packed         weight streaming on tcgen05 (M <= QUIK_STREAM_M_MAX, K_int % 32 == 0): the
  *                                    packed weights are widened on chip on their way to the tensor cores;
  *   q packed,       w packed         weight streaming on mma.sync, direct loads or TMA ring by QUIK_CFG_SMALL_M

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libquik_b200.so")
 
 QUIK_OK = 0
 F16, BF16 = 0, 1
-CFG_GEMM_ENGINE, CFG_TILE_N, CFG_SMALL_M, CFG_CTA_PAIR, CFG_PDL = 1, 2, 3, 4, 5
+CFG_GEMM_ENGINE, CFG_TILE_N, CFG_SMALL_M, CFG_CTA_PAIR, CFG_PDL, CFG_MMA_ISSUERS = 1, 2, 3, 4, 5, 6
 ENGINE_AUTO, ENGINE_TCGEN05, ENGINE_MMA_SYNC, ENGINE_TCGEN05_TS = 0, 1, 2, 3
 SMALL_M_MAX = 16       # most tokens of the mma.sync weight-streaming engines
 STREAM_M_MAX = 128     # most tokens of the tcgen05 weight-streaming engine
@@ -137,6 +137,11 @@ def set_small_m(mode) -> None:
     1 / True = weight streaming, engine by layer size, 2 = mma.sync fed by direct loads, 3 = tcgen05 fed by a TMA
     ring, 4 = mma.sync fed by a TMA ring."""
     check(load().quik_config_set(CFG_SMALL_M, int(mode)), "quik_config_set")
+
+
+def set_mma_issuers(n: int) -> None:
+    """1 or 2 threads issue the integer products of a tile (tcgen05 engine with both operands in shared memory)."""
+    check(load().quik_config_set(CFG_MMA_ISSUERS, int(n)), "quik_config_set")
 
 
 def set_pdl(on: bool) -> None:

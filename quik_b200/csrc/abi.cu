@@ -42,8 +42,8 @@ static int run_int8_gemm(const int8_t *A, const int8_t *B, int M, int N, int K, 
                          cudaStream_t st) {
   const int engine = g_engine.load();
   if (engine == QUIK_ENGINE_MMA_SYNC) return launch_gemm_mma_sync(A, B, M, N, K, ep, st);
-  if (engine == QUIK_ENGINE_TCGEN05) return launch_gemm_tcgen05(A, B, M, N, K, ep, st);
-  return launch_gemm_tcgen05_ts(A, 0, B, M, N, K, ep, st);
+  if (engine == QUIK_ENGINE_TCGEN05_TS) return launch_gemm_tcgen05_ts(A, 0, B, M, N, K, ep, st);
+  return launch_gemm_tcgen05(A, B, M, N, K, ep, st);
 }
 
 }  // namespace quik
@@ -98,6 +98,11 @@ int quik_config_set(int key, int value) {
     set_cta_pair(value);
     return QUIK_OK;
   }
+  if (key == QUIK_CFG_MMA_ISSUERS) {
+    if (value < 1 || value > 2) return QUIK_ERR_UNSUPPORTED;
+    set_mma_issuers(value);
+    return QUIK_OK;
+  }
   return QUIK_ERR_UNSUPPORTED;
 }
 
@@ -105,6 +110,7 @@ int quik_config_get(int key) {
   if (key == QUIK_CFG_SMALL_M) return g_small_m;
   if (key == QUIK_CFG_PDL) return g_pdl;
   if (key == QUIK_CFG_CTA_PAIR) return get_cta_pair();
+  if (key == QUIK_CFG_MMA_ISSUERS) return get_mma_issuers();
   if (key == QUIK_CFG_GEMM_ENGINE) return g_engine;
   if (key == QUIK_CFG_TILE_N) return get_tile_n();
   return QUIK_ERR_UNSUPPORTED;
@@ -115,8 +121,8 @@ int quik_device_status(int clear) { return device_status_read(clear); }
 int quik_gemm_plan(int M, int N, int K_int, int F, int *ctas, int *block_n) {
   if (M <= 0 || N <= 0 || K_int <= 0 || F < 0 || !ctas || !block_n) return QUIK_ERR_SHAPE;
   const int kblocks = (K_int + 127) / 128 + (F + 63) / 64;
-  if (g_engine.load() == QUIK_ENGINE_TCGEN05) choose_tile(M, N, kblocks, ctas, block_n);
-  else choose_tile_ts(M, N, kblocks, ctas, block_n);
+  if (g_engine.load() == QUIK_ENGINE_TCGEN05_TS) choose_tile_ts(M, N, kblocks, ctas, block_n);
+  else choose_tile(M, N, kblocks, ctas, block_n);
   return QUIK_OK;
 }
 
@@ -240,7 +246,7 @@ static int run_int4_gemm(const uint8_t *A, const uint8_t *B, int M, int N, int K
   int8_t *a8 = static_cast<int8_t *>(scratch);
   int8_t *b8 = a8 + align256((size_t)M * K);
   const int engine = g_engine.load();
-  const bool on_chip = (engine == QUIK_ENGINE_AUTO || engine == QUIK_ENGINE_TCGEN05_TS) && aligned16(A);
+  const bool on_chip = engine == QUIK_ENGINE_TCGEN05_TS && aligned16(A);
   int rc = launch_unpack_int4(B, b8, N, K, st);
   if (rc != QUIK_OK) return rc;
   if (on_chip) return launch_gemm_tcgen05_ts(A, 1, b8, M, N, K, ep, st);
@@ -324,7 +330,7 @@ int quik_mixed_linear_ld(const void *q, int q_packed, const void *w, int w_packe
   if (bits == 4 && q_packed && !w_packed) {
     // packed token codes against weights one per byte: tensor-core GEMM that widens the tokens on chip
     const int engine = g_engine.load();
-    if (engine != QUIK_ENGINE_AUTO && engine != QUIK_ENGINE_TCGEN05_TS) return QUIK_ERR_UNSUPPORTED;
+    if (engine != QUIK_ENGINE_TCGEN05_TS) return QUIK_ERR_UNSUPPORTED;
     if (K_int % 32 != 0) return QUIK_ERR_SHAPE;
     return launch_gemm_tcgen05_ts(q, 1, static_cast<const int8_t *>(w), M, N, K_int, ep, st);
   }

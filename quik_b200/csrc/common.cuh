@@ -118,6 +118,8 @@ void choose_tile(int M, int N, int kblocks, int *ctas_out, int *bn_out);
 void set_tile_n(int n);               // 0 = by shape, else a multiple of 16 in [32, 256]
 int get_tile_n();
 void set_cta_pair(int mode);           // 0 = by shape, 1 = never, 2 = always
+void set_mma_issuers(int n);           // 1 or 2 threads issue the integer products of a tile (shared-memory operand engine)
+int get_mma_issuers();
 int get_cta_pair();
 void set_debug_counters(void *buf);    // device buffer of 16 x uint64 per CTA, or NULL
 unsigned long long *get_debug_counters();

@@ -39,11 +39,13 @@ __device__ unsigned int g_device_status = 0;
 
 namespace {
 
-constexpr int NUM_THREADS = 320;              // TMA warp + MMA warp + 8 epilogue warps
+constexpr int NUM_THREADS = 352;              // TMA warp + MMA warp + 8 epilogue warps + second MMA warp
+constexpr int SECOND_ISSUER_WARP = 10;
 // Process-wide tuning knobs (quik_config_set): plain words, meant to be set once before the layers run; a
 // launch reads each of them once.
 std::atomic<int> g_tile_n{0};                                 // 0 = choose by shape, else a multiple of 16 in [32, 256]
 std::atomic<int> g_cta_pair{0};                               // 0 = by shape, 1 = never, 2 = always
+std::atomic<int> g_issuers{2};                                // threads that issue the integer products of a tile (1 or 2)
 std::atomic<unsigned long long *> g_dbg{nullptr};             // diagnostic counters (device memory), off by default
 
 // Shared-memory plan after the 1024-byte aligned ring of stages: 256 bytes of barriers etc. and the
@@ -100,7 +102,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint64_t *acc_empty = acc_full + 2;                                  // [2] region free again
   uint64_t *fp_full = acc_empty + 2;                                   // [2] outlier product complete
   uint64_t *fp_drained = fp_full + 2;                                  // [2] outlier product parked
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(fp_drained + 2);
+  uint64_t *int_started = fp_drained + 2;                              // [2] first integer k-block of the tile complete
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(int_started + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   // per-column epilogue vectors, one private copy per epilogue warp (no cross-warp barrier needed)
   float *s_vec = reinterpret_cast<float *>(aux + 256);                 // [8][3][HALF_CAP], 16-byte aligned
@@ -113,10 +116,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(full_bar + s), 1);
-      mbar_init(smem_u32(empty_bar + s), 1);
+      mbar_init(smem_u32(empty_bar + s), p.issuers);                 // every issuing thread commits the stage
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(acc_full + s), 1);
+      mbar_init(smem_u32(int_started + s), 1);
+      mbar_init(smem_u32(acc_full + s), p.issuers);
       mbar_init(smem_u32(acc_empty + s), NUM_EPI_THREADS * CTAS);    // epilogue threads of the whole pair
       mbar_init(smem_u32(fp_full + s), 1);
       mbar_init(smem_u32(fp_drained + s), NUM_EPI_THREADS * CTAS);
@@ -180,9 +184,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         feed(j, false, int_half, p.int_kb);
       }
     }
-  } else if (warp == 1) {
-    // ================= MMA issuer (pair leader only) =================
-    if (lane == 0 && rank == 0) {
+  } else if (warp == 1 || warp == SECOND_ISSUER_WARP) {
+    // ================= MMA issuers (pair leader only) =================
+    // One thread issues tcgen05.mma with both operands in shared memory no faster than every ~217 cycles (measured,
+    // whatever the instruction's size), the tensor pipe needs 128 for the largest one; two threads together reach
+    // ~153.  With p.issuers == 2 the threads share the integer k-blocks of a tile: thread 0 takes the 32-byte slices
+    // 0 and 2 of each block, thread 1 the slices 1 and 3, both into the tile's accumulator.  Integer sums do not
+    // depend on the order of their terms, and the tensor pipe applies the multiply-accumulates of one accumulator one
+    // after the other whoever issued them (no update is lost: tests/test_gpu_b_matmul.py holds exact products of
+    // long sums against the oracle for this mode).  What does need an order is kept on thread 0: the first block of a
+    // tile (its first instruction overwrites the accumulator; thread 1 waits until that block is complete before its
+    // first instruction of the tile) and the outlier product (floating point: one fixed order).
+    const int me = warp == 1 ? 0 : 1;
+    if (lane == 0 && rank == 0 && me < p.issuers) {
+      const bool shared_work = p.issuers == 2;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -193,7 +208,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t use_parity = (uint32_t)(j >> 1) & 1u;
         const uint32_t d = tmem_base + r * CAP_N;
         for (int kb = kb0; kb < kb1 && ok; ++kb) {
-          if (kb == 0) {
+          if (kb == 0 && me == 0) {
             // the region must be free: after the previous tile's epilogue (outlier product, or
             // integer product of an outlier-free layer), or after this tile's drain
             const bool after_drain = HAS_FP && !fp;
@@ -203,22 +218,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             w_region += clock64() - t0;
             tc_fence_after();
           }
+          if (!fp && kb == 1 && me == 1) {
+            if (!mbar_wait(smem_u32(int_started + r), use_parity, abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after();
+          }
           const long long t1 = clock64();
           if (!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag, p.status)) { ok = false; break; }
           w_full += clock64() - t1;
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+          const bool alone = !shared_work || fp || kb == 0;       // thread 0 issues the whole block
+          if (!alone || me == 0) {
 #pragma unroll
-          for (int k = 0; k < STAGE_K_BYTES / 32; ++k) {
-            // +32 bytes of K inside the swizzled row = +2 in the 16-byte start-address field
-            const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-            if (fp) mma_f16<CTAS>(d, da + 2 * k, db + 2 * k, p.idesc_fp, accumulate);
-            else mma_i8<CTAS>(d, da + 2 * k, db + 2 * k, p.idesc_int, accumulate);
+            for (int k = 0; k < STAGE_K_BYTES / 32; ++k) {
+              if (!alone && (k & 1) != me) continue;
+              // +32 bytes of K inside the swizzled row = +2 in the 16-byte start-address field
+              const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+              if (fp) mma_f16<CTAS>(d, da + 2 * k, db + 2 * k, p.idesc_fp, accumulate);
+              else mma_i8<CTAS>(d, da + 2 * k, db + 2 * k, p.idesc_int, accumulate);
+            }
           }
-          mma_commit<CTAS>(smem_u32(empty_bar + stage));    // stage reusable once these MMAs retire
+          if (shared_work && me == 0 && !fp && kb == 0) mma_commit<CTAS>(smem_u32(int_started + r));
+          mma_commit<CTAS>(smem_u32(empty_bar + stage));    // stage reusable once these MMAs retire (every issuer arrives)
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          if (fp && kb == p.fp_kb - 1) mma_commit<CTAS>(smem_u32(fp_full + r));
+          if (fp && kb == p.fp_kb - 1 && me == 0) mma_commit<CTAS>(smem_u32(fp_full + r));
           if (!fp && kb == p.int_kb - 1) mma_commit<CTAS>(smem_u32(acc_full + r));
         }
       };
@@ -228,7 +252,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (HAS_FP && j + 1 < n_local) issue(j + 1, true, 0, p.fp_kb);
         issue(j, false, int_half, p.int_kb);
       }
-      if (p.dbg) {
+      if (p.dbg && me == 0) {
         unsigned long long *d = p.dbg + (size_t)blockIdx.x * 16;
         d[0] = (unsigned long long)(clock64() - t_begin);   // MMA thread: issue loop
         d[1] = (unsigned long long)w_region;                // ... waiting for a free accumulator region
@@ -440,6 +464,8 @@ void set_tile_n(int n) { g_tile_n.store(n); }
 int get_tile_n() { return g_tile_n.load(); }
 void set_debug_counters(void *buf) { g_dbg.store(static_cast<unsigned long long *>(buf)); }
 unsigned long long *get_debug_counters() { return g_dbg.load(); }
+void set_mma_issuers(int n) { g_issuers.store(n); }
+int get_mma_issuers() { return g_issuers.load(); }
 void set_cta_pair(int mode) { g_cta_pair.store(mode); }
 int get_cta_pair() { return g_cta_pair.load(); }
 
@@ -480,6 +506,9 @@ int launch_gemm_tcgen05(const int8_t *A, const int8_t *B, int M, int N, int K, c
   p.idesc_int = make_idesc(2, 1, tile_m, block_n);                              // S32 accumulate, signed 8-bit operands
   p.idesc_fp = make_idesc(1, ep.dtype == QUIK_BF16 ? 1 : 0, tile_m, block_n);   // F32 accumulate, F16 / BF16 operands
   p.acc_shift = 0;
+  // two issuing threads only for long sums: a thread can run at most one ring of stages ahead of the other, which must
+  // stay well inside one tile for the per-tile barriers that both arrive on
+  p.issuers = (g_issuers.load() >= 2 && p.int_kb >= 16) ? 2 : 1;
 
   CUtensorMap ta, tb, tfa, tfb;
   int rc;

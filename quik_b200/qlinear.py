@@ -164,9 +164,9 @@ class MixedQLinear(torch.nn.Module):
         #   up to STREAM_M_MAX tokens: weight streaming, the weights stay in their storage format; the tcgen05
         #     streaming engine takes the token codes one per byte, the mma.sync engines (up to SMALL_M_MAX tokens, the
         #     default for 4-bit layers) packed like the weights;
-        #   more tokens: tensor-core GEMM on weight codes one per byte; 4-bit token codes stay packed (the reference
-        #     layout) and are widened on chip when the engine with the token operand in tensor memory is selected,
-        #     else the quantizer writes them one per byte.
+        #   more tokens: tensor-core GEMM on weight codes one per byte; the quantizer writes the token codes one per
+        #     byte too, except when the engine with the token operand in tensor memory is selected: it takes 4-bit
+        #     token codes packed (the reference layout) and widens them on chip.
         # (a packed 4-bit row must be a multiple of 16 bytes for these engines; otherwise both operands one per byte)
         small_m_mode = _lib.config_get(_lib.CFG_SMALL_M)
         row_ok = self.bits == 8 or self.int_features_num % 32 == 0
@@ -177,7 +177,7 @@ class MixedQLinear(torch.nn.Module):
             q_packed = M <= _lib.SMALL_M_MAX and small_m_mode != _lib.SMALL_M_TCGEN05
             w_packed = True
         else:
-            q_packed = row_ok and _lib.config_get(_lib.CFG_GEMM_ENGINE) in (_lib.ENGINE_AUTO, _lib.ENGINE_TCGEN05_TS)
+            q_packed = row_ok and _lib.config_get(_lib.CFG_GEMM_ENGINE) == _lib.ENGINE_TCGEN05_TS
             w_packed = False
         wide = not q_packed
         if shared_input.qint_x is not None and self.bits == 4 and shared_input.wide != wide:

@@ -79,6 +79,34 @@ def test_int8_matmul_writes_only_its_output(engine, M, N, K):
     assert bool((slab[:pad] == POISON).all()) and bool((slab[pad + M:] == POISON).all())
 
 
+@pytest.mark.parametrize("issuers", [1, 2])
+@pytest.mark.parametrize("tile,pair", [(0, 0), (256, 2), (256, 1), (240, 2), (128, 1)])
+@pytest.mark.parametrize("M,N,K", [(2048, 1024, 4096), (300, 520, 10752), (257, 264, 2048), (129, 4100, 28672)])
+def test_two_issuing_threads_give_the_exact_product(M, N, K, tile, pair, issuers):
+    """Long sums (K >= 2048) are issued by two threads that accumulate into one tensor-memory accumulator; the int32
+    result must still be the exact product (any lost or torn update would show), identical to one issuing thread's,
+    run after run.  Extreme codes (-128 / 127 mixed in) make every partial sum matter."""
+    import quik
+    g = torch.Generator().manual_seed(M + N + K + tile)
+    a = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8)
+    b = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8)
+    ref = kp.int8_matmul(a, b)
+    ad, bd = a.to(dev()), b.to(dev())
+    try:
+        _lib.set_engine(_lib.ENGINE_TCGEN05)
+        _lib.set_tile_n(tile)
+        _lib.set_cta_pair(pair)
+        _lib.set_mma_issuers(issuers)
+        for _ in range(3):
+            assert torch.equal(quik.matmul.int8Matmul(ad, bd).cpu(), ref)
+    finally:
+        _lib.set_engine(_lib.ENGINE_AUTO)
+        _lib.set_tile_n(0)
+        _lib.set_cta_pair(0)
+        _lib.set_mma_issuers(2)
+    assert_device_clean()
+
+
 @pytest.mark.parametrize("M,N,K", [(512, 32, 512), (64, 136, 3840), (2048, 512, 4096), (5, 24, 64)])
 def test_int4_matmul_exact(engine, M, N, K):
     """test/python/test_matmul.py:16-26 (first shape) and ragged / Llama-sized variants."""
