@@ -403,21 +403,32 @@ class LaunchTimer:
         return per
 
 
+def _hold_queue(ms):
+    """Keeps the stream busy for about `ms` milliseconds (a spinning kernel) so that launches enqueued meanwhile run
+    back to back afterwards: events around a launch then measure device time, not the host's launch rate."""
+    torch.cuda._sleep(int(ms * 1.9e6))
+
+
 def per_launch_roofline(wl, timer, seconds, sync_all):
-    """The steps launched eagerly with events around each launch of the layer kernel, for at least `seconds`."""
+    """The steps launched eagerly with events around each launch of the layer kernel, for at least `seconds`.  The
+    launches of a batch are enqueued behind a spinning kernel, so they start back to back whatever the host's speed."""
     wl.reset()
     sync_all()
-    for _ in range(2):
+    t0 = time.perf_counter()
+    for _ in range(3):
         wl.step()
+    host_per_step = (time.perf_counter() - t0) / 3
     sync_all()
+    batch = max(1, min(50, int(0.02 / max(host_per_step, 1e-5))))        # steps the host enqueues in ~20 ms
     timer.on = True
     t0 = time.perf_counter()
     n = 0
-    while n < 3 or (time.perf_counter() - t0 < seconds and n < 2000):
-        wl.step()
-        n += 1
-        if n % 20 == 0:
-            torch.cuda.synchronize()
+    while n < 3 or (time.perf_counter() - t0 < seconds and n < 4000):
+        _hold_queue(1.3 * batch * host_per_step * 1e3 + 1.0)
+        for _ in range(batch):
+            wl.step()
+        n += batch
+        torch.cuda.synchronize()
     sync_all()
     timer.on = False
     return timer.collect(), n
@@ -425,20 +436,24 @@ def per_launch_roofline(wl, timer, seconds, sync_all):
 
 def quantizer_times(wl, iters=30):
     """Activation-quantizer launches of the step's layers, CUDA events around each (the layers in turn, so the
-    inputs of one layer have left L2 before its next launch when the step's activations exceed it)."""
+    inputs of one layer have left L2 before its next launch when the step's activations exceed it); enqueued behind
+    a spinning kernel so that the events see device time only."""
     from quik_b200 import asymmetric
     mods = [c.module for c in wl.cases]
     res = {}
     evs = {i: [] for i in range(len(mods))}
-    for it in range(iters + 3):
+    ids = [m._idx16() for m in mods]
+    for i, (c, m) in enumerate(zip(wl.cases, mods)):
+        asymmetric.quantize_u16(c.x, ids[i][0], ids[i][1], m.bits, True)
+    torch.cuda.synchronize()
+    _hold_queue(25.0)
+    for it in range(iters):
         for i, (c, m) in enumerate(zip(wl.cases, mods)):
-            i16, f16 = m._idx16()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            asymmetric.quantize_u16(c.x, i16, f16, m.bits, True)
+            asymmetric.quantize_u16(c.x, ids[i][0], ids[i][1], m.bits, True)
             b.record()
-            if it >= 3:
-                evs[i].append((a, b))
+            evs[i].append((a, b))
     torch.cuda.synchronize()
     total_bytes, total_ms = 0.0, 0.0
     for i, (c, m) in enumerate(zip(wl.cases, mods)):

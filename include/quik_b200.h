@@ -63,10 +63,11 @@ extern "C" {
  * it waits for the predecessor's completion before its first global load or store, so results are those of
  * plain stream order; 0 launches in plain stream order. */
 #define QUIK_CFG_PDL           5
-/* Threads that issue the integer products of a tile in the tcgen05 engine with both operands in shared memory: 2
- * (default) two threads share the k-slices of every block of a long sum (K_int >= 2048) and accumulate into the same
- * tensor-memory accumulator -- one thread cannot issue these instructions as fast as the tensor pipe executes them;
- * integer sums do not depend on the order of their terms; 1 a single thread issues everything. */
+/* Threads that issue the integer products of a tile in the tcgen05 engine with both operands in shared memory: 1
+ * (default) a single thread issues everything; 2 two threads share the k-slices of every block of a long sum
+ * (K_int >= 2048) and accumulate into the same tensor-memory accumulator (integer sums do not depend on the order of
+ * their terms; the outlier product stays on one thread).  One thread cannot issue these instructions as fast as the
+ * tensor pipe could execute them, but under the board's power limit the second thread was measured to gain 1-2 %. */
 #define QUIK_CFG_MMA_ISSUERS   6
 
 const char *quik_version(void);
@@ -85,6 +86,11 @@ int quik_gemm_plan(int M, int N, int K_int, int F, int *ctas, int *block_n);
  * per-device status word and returns early.  This call synchronises the current device, returns
  * QUIK_OK or QUIK_ERR_DEVICE_WAIT, and clears the word when `clear` is non-zero. */
 int quik_device_status(int clear);
+/* Self-test of that mechanism (no reference counterpart): launches a one-CTA kernel that waits on a barrier nothing
+ * arrives on, for at most limit_us microseconds (1 .. 1,000,000).  The wait gives up like the waits of the product
+ * kernels do: the kernel returns normally, *device_result (an int in device memory, may be NULL) is set to 2, and the
+ * next quik_device_status call reports QUIK_ERR_DEVICE_WAIT.  Nothing faults or hangs. */
+int quik_selftest_bounded_wait(unsigned int limit_us, int *device_result, void *stream);
 /* Diagnostics: when `device_buffer` (16 x uint64 per launched CTA, caller-owned device memory) is
  * non-NULL, every tcgen05 GEMM launch writes per-CTA cycle counters there: [0] MMA issue loop,
  * [1] of which waiting for a free accumulator region, [2] waiting for operands, [3] tiles of the CTA,
@@ -118,6 +124,25 @@ int quik_asym_quantize_u16(const void *src, int dtype, int rows, int cols,
                            const uint16_t *int_indices, int num_int,
                            const uint16_t *fp_indices, int num_fp, int bits, int wide,
                            void *dst, void *meta, void *fp_x, void *stream);
+
+/* The same quantizer with the producer of its input fused in, so that the normalised / activated matrix never
+ * goes to HBM.  No counterpart in the reference, which quantizes whatever tensor the decoder layer hands to the linear
+ * (experiments/qlinear.py:114-117); these cover the two producers of a Llama decoder layer (the groups of
+ * experiments/llama.py:402-407): the RMSNorm in front of q/k/v and of gate/up, and SiLU(gate) * up in front of
+ * down_proj.  Outputs exactly as quik_asym_quantize_u16 on the produced matrix:
+ *   rmsnorm:   y[r,c] = T(float(x[r,c]) * rsqrt(mean_c(x[r,:]^2) + eps)) * norm_weight[c]   (fp32 statistics, rounded
+ *              to T, multiplied by the weight in T: the arithmetic of LlamaRMSNorm)
+ *   silu_mul:  y[r,c] = T(silu(float(gate[r,c]))) * up[r,c]                                  (both roundings as
+ *              torch's F.silu(gate) * up)
+ * x, gate, up [rows, cols] dtype; norm_weight [cols] dtype. */
+int quik_rmsnorm_quantize_u16(const void *x, const void *norm_weight, float eps, int dtype, int rows, int cols,
+                              const uint16_t *int_indices, int num_int,
+                              const uint16_t *fp_indices, int num_fp, int bits, int wide,
+                              void *dst, void *meta, void *fp_x, void *stream);
+int quik_silu_mul_quantize_u16(const void *gate, const void *up, int dtype, int rows, int cols,
+                               const uint16_t *int_indices, int num_int,
+                               const uint16_t *fp_indices, int num_fp, int bits, int wide,
+                               void *dst, void *meta, void *fp_x, void *stream);
 
 /* quik.asymmetric.find_meta (src/asymmetric/asymmetric.cpp:40-44, asymmetric.cu:263-338):
  * meta[2r] = T(fmaxf((max_r - min_r) / (2^bits - 1), 1e-6f)), meta[2r+1] = min_r. */

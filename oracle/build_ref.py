@@ -1,11 +1,13 @@
 """Build oracle/_ref/quik_ref_ops*.so: the QUIK reference's own CUDA kernels.
 
-Test infrastructure, not product code.  The reference's sources are compiled where they lie (the checkout given by
-QUIK_REFERENCE_DIR, default /root/reference): src/asymmetric/{asymmetric,fused_dequantize}.cu,
+Test infrastructure, not product code.  The reference's sources are compiled where they lie (the checkout given by the
+environment variable QUIK_REFERENCE_DIR, else a directory `reference` beside this repository): src/asymmetric/{asymmetric,fused_dequantize}.cu,
 src/symmetric/{symmetric,fused_dequantize}.cu and src/matmul/matmul.cu with the small binding oracle/ref_binding.cpp,
 by nvcc directly (not by the reference's cmake build).  They need CUTLASS headers (the reference's own submodule is not
 vendored in the checkout); a CUTLASS header tree installed in the Python environment is used instead.  The cuSPARSELt
-path is not enabled.  Nothing of the reference is copied into this repository; the output directory is git-ignored.
+path is not enabled.  The reference's module file experiments/qlinear.py is placed unmodified next to the library
+(reference_qlinear.py) so that a GPU test can run it against this repository's `quik` package.  Nothing of the reference
+enters this repository's history: the output directory is git-ignored.
 
 Usage: python oracle/build_ref.py     (prints the path of the library, or why it was not built, and exits 0)
 """
@@ -40,8 +42,27 @@ def lib_path():
     return os.path.join(OUT_DIR, NAME + sysconfig.get_config_var("EXT_SUFFIX"))
 
 
+def reference_dir():
+    """The reference checkout: QUIK_REFERENCE_DIR, else `reference` beside this repository (may not exist)."""
+    return os.environ.get("QUIK_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def module_path():
+    return os.path.join(OUT_DIR, "reference_qlinear.py")
+
+
+def _place_module(ref):
+    """The reference's layer module, byte for byte, beside the library (kept out of history with it)."""
+    src = os.path.join(ref, "experiments", "qlinear.py")
+    if os.path.isfile(src):
+        import shutil
+        os.makedirs(OUT_DIR, exist_ok=True)
+        shutil.copyfile(src, module_path())
+
+
 def build(verbose=False):
-    ref = os.environ.get("QUIK_REFERENCE_DIR", "/root/reference")
+    ref = reference_dir()
+    _place_module(ref)
     srcs = [os.path.join(ref, "src", *p) for p in (("asymmetric", "asymmetric.cu"), ("asymmetric", "fused_dequantize.cu"),
                                                    ("symmetric", "symmetric.cu"), ("symmetric", "fused_dequantize.cu"),
                                                    ("matmul", "matmul.cu"))]

@@ -32,8 +32,11 @@ SIGNATURES = {
     "quik_device_status": (_i, [_i]),
     "quik_gemm_plan": (_i, [_i, _i, _i, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "quik_debug_counters": (_i, [_vp]),
+    "quik_selftest_bounded_wait": (_i, [ctypes.c_uint, _vp, _vp]),
     "quik_asym_quantize": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp]),
     "quik_asym_quantize_u16": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "quik_rmsnorm_quantize_u16": (_i, [_vp, _vp, _f, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "quik_silu_mul_quantize_u16": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "quik_asym_find_meta": (_i, [_vp, _i, _i, _i, _i, _vp, _vp]),
     "quik_asym_quantize_old": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _vp]),
     "quik_asym_dequantize": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),

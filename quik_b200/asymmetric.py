@@ -65,6 +65,53 @@ def quantize_u16(src, int_indices_u16, fp_indices_u16, bits, wide):
     return dst, meta, fp_x
 
 
+def _alloc_quantized(src, num_int, num_fp, bits, wide):
+    rows = src.shape[0]
+    if bits == 4 and not wide:
+        dst = torch.empty((rows, num_int // 2), dtype=torch.uint8, device=src.device)
+    else:
+        dst = torch.empty((rows, num_int), dtype=torch.int8, device=src.device)
+    meta = torch.empty((2 * rows,), dtype=src.dtype, device=src.device)
+    fp_x = torch.empty((rows, num_fp), dtype=src.dtype, device=src.device)
+    return dst, meta, fp_x
+
+
+def rmsnorm_quantize_u16(x, norm_weight, eps, int_indices_u16, fp_indices_u16, bits, wide):
+    """quantize_u16(rmsnorm(x) * norm_weight) in one pass over ``x``: the normalised matrix is never written
+    (LlamaRMSNorm arithmetic: fp32 statistics, rounded to x.dtype, times the weight in x.dtype)."""
+    require_cuda_contiguous("rmsnorm_quantize", x=x, norm_weight=norm_weight, int_indices=int_indices_u16,
+                            fp_indices=fp_indices_u16)
+    _check_bits(bits)
+    rows, cols = x.shape
+    if norm_weight.numel() != cols or norm_weight.dtype != x.dtype:
+        raise RuntimeError("rmsnorm_quantize: norm_weight must have one entry per column, of x's dtype")
+    num_int, num_fp = int_indices_u16.numel(), fp_indices_u16.numel()
+    with torch.cuda.device(x.device):
+        dst, meta, fp_x = _alloc_quantized(x, num_int, num_fp, bits, wide)
+        check(load().quik_rmsnorm_quantize_u16(ptr(x), ptr(norm_weight), float(eps), dtype_code(x.dtype), rows, cols,
+                                               ptr(int_indices_u16), num_int, ptr(fp_indices_u16), num_fp, bits,
+                                               int(bool(wide)), ptr(dst), ptr(meta), ptr(fp_x), stream_of(x)),
+              "rmsnorm_quantize")
+    return dst, meta, fp_x
+
+
+def silu_mul_quantize_u16(gate, up, int_indices_u16, fp_indices_u16, bits, wide):
+    """quantize_u16(silu(gate) * up) in one pass over ``gate`` and ``up``: the activated matrix is never written."""
+    require_cuda_contiguous("silu_mul_quantize", gate=gate, up=up, int_indices=int_indices_u16, fp_indices=fp_indices_u16)
+    _check_bits(bits)
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise RuntimeError("silu_mul_quantize: gate and up must have the same shape and dtype")
+    rows, cols = gate.shape
+    num_int, num_fp = int_indices_u16.numel(), fp_indices_u16.numel()
+    with torch.cuda.device(gate.device):
+        dst, meta, fp_x = _alloc_quantized(gate, num_int, num_fp, bits, wide)
+        check(load().quik_silu_mul_quantize_u16(ptr(gate), ptr(up), dtype_code(gate.dtype), rows, cols,
+                                                ptr(int_indices_u16), num_int, ptr(fp_indices_u16), num_fp, bits,
+                                                int(bool(wide)), ptr(dst), ptr(meta), ptr(fp_x), stream_of(gate)),
+              "silu_mul_quantize")
+    return dst, meta, fp_x
+
+
 def find_meta(src, bits):
     """meta = find_meta(src, bits); asymmetric.cpp:40-44 (flat [2*rows], (scale, zero) interleaved)."""
     if not src.is_cuda:

@@ -1,8 +1,10 @@
 """One Llama-2-style decoder block whose seven linear layers are MixedQLinear modules, wired the way the
 reference wires them (QUIK experiments/llama.py:394-440): q/k/v share one quantized input (group of 3),
-gate/up share one (group of 2), o and down quantize on their own; down_proj may run in 8 bits
-(``int8_down_proj``).  RMSNorm, rotary embedding and attention are plain torch (``F.scaled_dot_product_attention``);
-they are the callers on either side of the hot path, not part of it.  Weights are random (seeded) and
+gate/up share one (group of 2), o and down quantize on their own (groups of 1); down_proj may run in 8 bits
+(``int8_down_proj``).  Rotary embedding and attention are plain torch (``F.scaled_dot_product_attention``): they are
+the callers on either side of the hot path, not part of it.  The producers of the quantizers' inputs are fused into
+the quantizer (``fused_producers``, default on): RMSNorm -> quantize for q/k/v and gate/up, SiLU(gate) * up -> quantize
+for down_proj, each one pass over its input with the normalised / activated matrix never written to HBM.  Weights are random (seeded) and
 quantized per output channel by symmetric round-to-nearest with clipping search, outlier columns are seed-chosen.
 """
 from __future__ import annotations
@@ -19,7 +21,7 @@ from .workloads import rtn_clip_scales
 class QuikLlamaBlock(torch.nn.Module):
     def __init__(self, hidden=4096, heads=32, intermediate=11008, kv_heads=None, bits=4, down_bits=8,
                  fp_features=256, seed=0, device="cuda", dtype=torch.float16, eps=1e-5, rope_theta=10000.0,
-                 clip=True, keep_dense=False):
+                 clip=True, keep_dense=False, fused_producers=True):
         super().__init__()
         kv_heads = kv_heads or heads
         self.hidden, self.heads, self.kv_heads, self.head_dim = hidden, heads, kv_heads, hidden // heads
@@ -29,6 +31,9 @@ class QuikLlamaBlock(torch.nn.Module):
         # shared quantized inputs, in the reference's call order [k, v, q] and [up, gate]
         self.qkv_shared = SharedQuantizedInput(3)
         self.mlp_shared = SharedQuantizedInput(2)
+        self.o_shared = SharedQuantizedInput(1)
+        self.down_shared = SharedQuantizedInput(1)
+        self.fused_producers = fused_producers
         dense = {}
         # the members of a group must agree on the outlier columns (the cached quantized input is shared):
         # each member draws them from a generator seeded per group
@@ -42,10 +47,11 @@ class QuikLlamaBlock(torch.nn.Module):
             mods[name], dense[name] = self._member(hidden, out_f, bits, fp_features, perm_gen, g, device, dtype,
                                                    self.mlp_shared, clip)
         perm_gen = torch.Generator().manual_seed(seed + 3)
-        mods["o_proj"], dense["o_proj"] = self._member(hidden, hidden, bits, fp_features, perm_gen, g, device, dtype, None, clip)
+        mods["o_proj"], dense["o_proj"] = self._member(hidden, hidden, bits, fp_features, perm_gen, g, device, dtype,
+                                                       self.o_shared, clip)
         perm_gen = torch.Generator().manual_seed(seed + 4)
         mods["down_proj"], dense["down_proj"] = self._member(intermediate, hidden, down_bits, fp_features, perm_gen, g,
-                                                             device, dtype, None, clip)
+                                                             device, dtype, self.down_shared, clip)
         for k, v in mods.items():
             setattr(self, k, v)
         self.dense = dense if keep_dense else None       # fake-quantized fp weights, for reference checks
@@ -107,7 +113,15 @@ class QuikLlamaBlock(torch.nn.Module):
         lin = linear or (lambda name, t: getattr(self, name)(t))
         b, s, _ = x.shape
         fused = linear is None and self._fused_groups is not None
-        h = self._rms_norm(x, self.input_norm)
+        # producers fused into the quantizers: only with the quantized layers in place, their fused forward, and the
+        # member-wise groups (the stacked copies have no shared input)
+        prod = (linear is None and self.fused_producers and not fused
+                and all(getattr(self, n).fused for n in ("k_proj", "up_proj", "down_proj")))
+        if prod:
+            self.k_proj.quantize_rmsnorm(x, self.input_norm, self.eps)      # fills the q/k/v group's shared input
+            h = x                                                           # only its shape is used below
+        else:
+            h = self._rms_norm(x, self.input_norm)
         if fused:
             k, v, q = self._fused_groups[0](h).split(self._qkv_sizes, dim=-1)
         else:
@@ -124,11 +138,19 @@ class QuikLlamaBlock(torch.nn.Module):
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=1.0 / math.sqrt(self.head_dim))
         a = a.transpose(1, 2).reshape(b, s, self.hidden)
         x = x + lin("o_proj", a)
-        h = self._rms_norm(x, self.post_norm)
+        if prod:
+            self.up_proj.quantize_rmsnorm(x, self.post_norm, self.eps)
+            h = x
+        else:
+            h = self._rms_norm(x, self.post_norm)
         if fused:
             up, gate = self._fused_groups[1](h).split(self.up_proj.out_features, dim=-1)
         else:
             up = lin("up_proj", h)
             gate = lin("gate_proj", h)
-        x = x + lin("down_proj", F.silu(gate) * up)
+        if prod:
+            self.down_proj.quantize_silu_mul(gate, up)
+            x = x + lin("down_proj", gate)                                  # `gate` only gives the shape
+        else:
+            x = x + lin("down_proj", F.silu(gate) * up)
         return x

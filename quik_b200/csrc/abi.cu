@@ -126,6 +126,11 @@ int quik_gemm_plan(int M, int N, int K_int, int F, int *ctas, int *block_n) {
   return QUIK_OK;
 }
 
+int quik_selftest_bounded_wait(unsigned int limit_us, int *device_result, void *stream) {
+  if (limit_us == 0 || limit_us > 1000000u) return QUIK_ERR_SHAPE;
+  return launch_bounded_wait_selftest(limit_us, device_result, static_cast<cudaStream_t>(stream));
+}
+
 int quik_debug_counters(void *device_buffer) {
   set_debug_counters(device_buffer);
   return QUIK_OK;
@@ -161,6 +166,26 @@ int quik_asym_quantize_u16(const void *src, int dtype, int rows, int cols, const
   if (rc != QUIK_OK) return rc;
   return launch_asym_quantize(src, dtype, rows, cols, int_indices, num_int, fp_indices, num_fp, 2, bits, wide, dst,
                               meta, fp_x, static_cast<cudaStream_t>(stream));
+}
+
+int quik_rmsnorm_quantize_u16(const void *x, const void *norm_weight, float eps, int dtype, int rows, int cols,
+                              const uint16_t *int_indices, int num_int, const uint16_t *fp_indices, int num_fp, int bits,
+                              int wide, void *dst, void *meta, void *fp_x, void *stream) {
+  int rc = check_quantize_args(x, dtype, rows, cols, int_indices, num_int, fp_indices, num_fp, bits, dst, meta, fp_x);
+  if (rc != QUIK_OK) return rc;
+  if (rows > 0 && !norm_weight) return QUIK_ERR_NULL;
+  return launch_asym_quantize_fused(1, x, norm_weight, eps, dtype, rows, cols, int_indices, num_int, fp_indices, num_fp,
+                                    bits, wide, dst, meta, fp_x, static_cast<cudaStream_t>(stream));
+}
+
+int quik_silu_mul_quantize_u16(const void *gate, const void *up, int dtype, int rows, int cols,
+                               const uint16_t *int_indices, int num_int, const uint16_t *fp_indices, int num_fp, int bits,
+                               int wide, void *dst, void *meta, void *fp_x, void *stream) {
+  int rc = check_quantize_args(gate, dtype, rows, cols, int_indices, num_int, fp_indices, num_fp, bits, dst, meta, fp_x);
+  if (rc != QUIK_OK) return rc;
+  if (rows > 0 && !up) return QUIK_ERR_NULL;
+  return launch_asym_quantize_fused(2, gate, up, 0.f, dtype, rows, cols, int_indices, num_int, fp_indices, num_fp, bits,
+                                    wide, dst, meta, fp_x, static_cast<cudaStream_t>(stream));
 }
 
 int quik_asym_find_meta(const void *src, int dtype, int rows, int cols, int bits, void *meta, void *stream) {

@@ -156,6 +156,10 @@ __device__ __forceinline__ float warp_min(float v) {
 int launch_asym_quantize(const void *src, int dtype, int rows, int cols, const void *int_idx,
                          int num_int, const void *fp_idx, int num_fp, int idx_bytes, int bits,
                          int wide, void *dst, void *meta, void *fp_x, cudaStream_t st);
+// quantizer with the producer of X fused in (quantize.cu): prod 1 = RMSNorm (aux = weight vector), 2 = SiLU(src) * aux
+int launch_asym_quantize_fused(int prod, const void *src, const void *aux, float eps, int dtype, int rows, int cols,
+                               const void *int_idx, int num_int, const void *fp_idx, int num_fp, int bits, int wide,
+                               void *dst, void *meta, void *fp_x, cudaStream_t st);
 int launch_find_meta(const void *src, int dtype, int rows, int cols, int bits, void *meta,
                      cudaStream_t st);
 int launch_quantize_old(const void *src, int dtype, const void *meta, int rows, int cols, int bits,
@@ -168,6 +172,7 @@ int launch_asym_dequantize(const int32_t *x, const void *meta, const void *scale
 int launch_sym_dequantize(const void *x, int x_bits, const void *scale_row, const void *scale_col,
                           const void *y, void *out, int rows, int cols, cudaStream_t st);
 int launch_unpack_int4(const uint8_t *src, int8_t *dst, int rows, int cols, cudaStream_t st);
+int launch_bounded_wait_selftest(unsigned int limit_us, int *result, cudaStream_t st);   // selftest.cu
 
 // Epilogue description shared by the GEMM engines.
 struct Epilogue {

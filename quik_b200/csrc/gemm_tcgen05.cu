@@ -45,7 +45,7 @@ constexpr int SECOND_ISSUER_WARP = 10;
 // launch reads each of them once.
 std::atomic<int> g_tile_n{0};                                 // 0 = choose by shape, else a multiple of 16 in [32, 256]
 std::atomic<int> g_cta_pair{0};                               // 0 = by shape, 1 = never, 2 = always
-std::atomic<int> g_issuers{2};                                // threads that issue the integer products of a tile (1 or 2)
+std::atomic<int> g_issuers{1};                                // threads that issue the integer products of a tile (1 or 2)
 std::atomic<unsigned long long *> g_dbg{nullptr};             // diagnostic counters (device memory), off by default
 
 // Shared-memory plan after the 1024-byte aligned ring of stages: 256 bytes of barriers etc. and the
@@ -188,7 +188,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ================= MMA issuers (pair leader only) =================
     // One thread issues tcgen05.mma with both operands in shared memory no faster than every ~217 cycles (measured,
     // whatever the instruction's size), the tensor pipe needs 128 for the largest one; two threads together reach
-    // ~153.  With p.issuers == 2 the threads share the integer k-blocks of a tile: thread 0 takes the 32-byte slices
+    // ~153 in isolation.  Inside this kernel the second thread gains 1-2 % only (the GPU runs into its power limit and
+    // lowers the clock instead), so one thread is the default and two are an option (QUIK_CFG_MMA_ISSUERS).
+    // With p.issuers == 2 the threads share the integer k-blocks of a tile: thread 0 takes the 32-byte slices
     // 0 and 2 of each block, thread 1 the slices 1 and 3, both into the tile's accumulator.  Integer sums do not
     // depend on the order of their terms, and the tensor pipe applies the multiply-accumulates of one accumulator one
     // after the other whoever issued them (no update is lost: tests/test_gpu_b_matmul.py holds exact products of

@@ -83,16 +83,25 @@ __device__ __forceinline__ void emit_codes(const uint32_t (&c)[4], uint32_t &w0,
 // IdxT: int64_t (reference ABI) or uint16_t (layer-cached ids).
 // NC = register-cached chunks per thread (6 covers rows of up to 12288 integer columns; longer rows gather twice)
 
-template <typename T, int BITS, bool WIDE, typename IdxT, int NC, int NTHR>
+//
+// PROD: what produces the row that is quantized (the producer of X fused into the quantizer, so that the intermediate
+// never goes to HBM; the callers on the input side of the layer, QUIK experiments/llama.py:402-407):
+//   0  the row of `src` as it is (quik.asymmetric.quantize);
+//   1  RMSNorm of the row: T(float(x) * rsqrt(mean(x^2) + eps)) * aux[col]   (aux = the norm's weight vector;
+//      the arithmetic of LlamaRMSNorm: normalise in fp32, round to T, multiply by the weight in T);
+//   2  SiLU(src) * aux: T(silu(float(g))) * u with g = src[row, col], u = aux[row, col] (aux = a second matrix,
+//      the MLP's `up` output beside its `gate` output), both roundings as torch's F.silu(gate) * up.
+template <typename T, int BITS, bool WIDE, typename IdxT, int NC, int NTHR, int PROD>
 __global__ void __launch_bounds__(NTHR)
 asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int_idx,
                          const IdxT *__restrict__ fp_idx, int rows, int cols, int num_int, int num_fp,
                          uint8_t *__restrict__ dst, T *__restrict__ meta, T *__restrict__ fp_x,
-                         int vec_load, int vec_store, int vec_ids, int nbuf) {
+                         int vec_load, int vec_store, int vec_ids, int nbuf, const T *__restrict__ aux, float eps) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ float s_red[2][NTHR / 32];
   const int cols_pad = (cols + 7) & ~7;
   T *s_buf = reinterpret_cast<T *>(smem_raw);          // two row buffers: the next row loads while this one is used
+  T *s_aux = s_buf + (size_t)nbuf * cols_pad;          // PROD == 2: the same for the rows of the second matrix
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int num_chunks = (num_int + 7) >> 3;
   constexpr bool kPacked = BITS == 4 && !WIDE;
@@ -103,6 +112,12 @@ asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int
     const uint4 *g = reinterpret_cast<const uint4 *>(src + (size_t)r * cols);
     for (int i = tid; i < (cols >> 3); i += NTHR)
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sbase + i * 16), "l"(g + i));
+    if (PROD == 2) {
+      const unsigned abase = (unsigned)__cvta_generic_to_shared(s_aux + (size_t)buf * cols_pad);
+      const uint4 *ga = reinterpret_cast<const uint4 *>(aux + (size_t)r * cols);
+      for (int i = tid; i < (cols >> 3); i += NTHR)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(abase + i * 16), "l"(ga + i));
+    }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
   // ids of chunk c as four words of two 16-bit ids; the pad of the last chunk repeats the first id
@@ -145,6 +160,38 @@ asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int
     __syncthreads();
     const T *row = src + (size_t)r * cols;
     for (int i = tid; i < cols; i += NTHR) s_row[i] = row[i];
+    if (PROD == 2) {
+      const T *arow = aux + (size_t)r * cols;
+      T *s_arow = s_aux + (size_t)buf * cols_pad;
+      for (int i = tid; i < cols; i += NTHR) s_arow[i] = arow[i];
+    }
+    __syncthreads();
+  }
+
+  // ---- the producer of X, applied to the row in shared memory
+  if (PROD == 1) {
+    float ss = 0.f;
+    for (int i = tid; i < cols; i += NTHR) {
+      const float f = Traits<T>::to_float(s_row[i]);
+      ss = fmaf(f, f, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) s_red[0][warp] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int w = 0; w < NTHR / 32; ++w) ss += s_red[0][w];
+    const float rstd = rsqrtf(ss / (float)cols + eps);
+    for (int i = tid; i < cols; i += NTHR)
+      s_row[i] = __hmul(Traits<T>::from_float(Traits<T>::to_float(s_row[i]) * rstd), aux[i]);
+    __syncthreads();            // the transformed row is complete; s_red may be written again
+  } else if (PROD == 2) {
+    const T *s_arow = s_aux + (size_t)buf * cols_pad;
+    for (int i = tid; i < cols; i += NTHR) {
+      const float g = Traits<T>::to_float(s_row[i]);
+      s_row[i] = __hmul(Traits<T>::from_float(g / (1.f + expf(-g))), s_arow[i]);
+    }
     __syncthreads();
   }
 
@@ -275,14 +322,21 @@ asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int
   }
 }
 
-template <typename T, int BITS, bool WIDE, typename IdxT, int NC, int NTHR>
+struct RowProducer {
+  const void *aux;     // PROD 1: norm weight [cols]; PROD 2: second matrix [rows, cols]
+  float eps;
+};
+
+template <typename T, int BITS, bool WIDE, typename IdxT, int NC, int NTHR, int PROD>
 int launch_asym_rows_nc(const void *src, int rows, int cols, const void *int_idx, int num_int,
-                     const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x, cudaStream_t st) {
+                     const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x, const RowProducer &pr,
+                     cudaStream_t st) {
   const size_t row_bytes = (size_t)((cols + 7) & ~7) * sizeof(T);
-  const int nbuf = 2 * row_bytes <= 200 * 1024 ? 2 : 1;
-  const size_t smem = nbuf * row_bytes;
+  constexpr int kMats = PROD == 2 ? 2 : 1;              // matrices whose rows are staged in shared memory
+  const int nbuf = 2 * kMats * row_bytes <= 200 * 1024 ? 2 : 1;
+  const size_t smem = nbuf * kMats * row_bytes;
   if (smem > 200 * 1024) return QUIK_ERR_UNSUPPORTED;
-  auto kern = asym_quantize_row_kernel<T, BITS, WIDE, IdxT, NC, NTHR>;
+  auto kern = asym_quantize_row_kernel<T, BITS, WIDE, IdxT, NC, NTHR, PROD>;
   // shared-memory opt-in and occupancy: once per (instantiation, device, shared-memory size)
   static PerDeviceSmem state;
   int cached_per_sm = 0;
@@ -291,7 +345,7 @@ int launch_asym_rows_nc(const void *src, int rows, int cols, const void *int_idx
     if (rc != QUIK_OK) return rc;
   }
   const int grid = min(rows, num_sms() * cached_per_sm);
-  const int vec_load = (cols % 8 == 0) && aligned16(src);
+  const int vec_load = (cols % 8 == 0) && aligned16(src) && (PROD != 2 || aligned16(pr.aux));
   const bool packed = (BITS == 4 && !WIDE);
   const int vec_store = (num_int % 8 == 0) && ((reinterpret_cast<uintptr_t>(dst) & (packed ? 3u : 7u)) == 0);
   const int vec_ids = sizeof(IdxT) == 2 && (num_int % 8 == 0) && aligned16(int_idx);
@@ -299,44 +353,46 @@ int launch_asym_rows_nc(const void *src, int rows, int cols, const void *int_idx
   QUIK_CUDA_TRY(cudaLaunchKernelEx(&lc.cfg, kern, static_cast<const T *>(src), static_cast<const IdxT *>(int_idx),
                                    static_cast<const IdxT *>(fp_idx), rows, cols, num_int, num_fp,
                                    static_cast<uint8_t *>(dst), static_cast<T *>(meta), static_cast<T *>(fp_x),
-                                   vec_load, vec_store, vec_ids, nbuf));
+                                   vec_load, vec_store, vec_ids, nbuf, static_cast<const T *>(pr.aux), pr.eps));
   return check_launch("asym_quantize_row_kernel");
 }
 
-template <typename T, int BITS, bool WIDE, typename IdxT, int NTHR>
+template <typename T, int BITS, bool WIDE, typename IdxT, int NTHR, int PROD>
 int launch_asym_rows_thr(const void *src, int rows, int cols, const void *int_idx, int num_int,
-                         const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x, cudaStream_t st) {
+                         const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x, const RowProducer &pr,
+                         cudaStream_t st) {
   const int per_thread = (((num_int + 7) >> 3) + NTHR - 1) / NTHR;
   if (per_thread <= 2)
-    return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 2, NTHR>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+    return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 2, NTHR, PROD>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
   if (per_thread <= 4)
-    return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 4, NTHR>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
-  return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 6, NTHR>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+    return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 4, NTHR, PROD>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
+  return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 6, NTHR, PROD>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
 }
 
 // With fewer rows than SMs the row's latency is all there is: 512 threads per row (measured 2.6 / 3.4 us against
 // 2.9 / 4.1 us for 16 rows of 4096 / 11008 columns); with many rows 256 threads give more rows in flight per SM
 // (10.9 / 21 us against 13.9 / 25.8 us for 2048 rows).
-template <typename T, int BITS, bool WIDE, typename IdxT>
+template <typename T, int BITS, bool WIDE, typename IdxT, int PROD>
 int launch_asym_rows(const void *src, int rows, int cols, const void *int_idx, int num_int,
-                     const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x, cudaStream_t st) {
+                     const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x, const RowProducer &pr,
+                     cudaStream_t st) {
   if (rows <= num_sms())
-    return launch_asym_rows_thr<T, BITS, WIDE, IdxT, 2 * kQuantThreads>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
-  return launch_asym_rows_thr<T, BITS, WIDE, IdxT, kQuantThreads>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+    return launch_asym_rows_thr<T, BITS, WIDE, IdxT, 2 * kQuantThreads, PROD>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
+  return launch_asym_rows_thr<T, BITS, WIDE, IdxT, kQuantThreads, PROD>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
 }
 
-template <typename T, typename IdxT>
+template <typename T, typename IdxT, int PROD>
 int dispatch_bits(int bits, int wide, const void *src, int rows, int cols, const void *int_idx,
                   int num_int, const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x,
-                  cudaStream_t st) {
+                  const RowProducer &pr, cudaStream_t st) {
   if (bits == 8)
-    return launch_asym_rows<T, 8, true, IdxT>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
-                                           meta, fp_x, st);
+    return launch_asym_rows<T, 8, true, IdxT, PROD>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
+                                                    meta, fp_x, pr, st);
   if (wide)
-    return launch_asym_rows<T, 4, true, IdxT>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
-                                           meta, fp_x, st);
-  return launch_asym_rows<T, 4, false, IdxT>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
-                                          meta, fp_x, st);
+    return launch_asym_rows<T, 4, true, IdxT, PROD>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
+                                                    meta, fp_x, pr, st);
+  return launch_asym_rows<T, 4, false, IdxT, PROD>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst,
+                                                   meta, fp_x, pr, st);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -428,14 +484,35 @@ int launch_asym_quantize(const void *src, int dtype, int rows, int cols, const v
                          int num_int, const void *fp_idx, int num_fp, int idx_bytes, int bits,
                          int wide, void *dst, void *meta, void *fp_x, cudaStream_t st) {
   if (rows == 0) return QUIK_OK;
+  const RowProducer none{nullptr, 0.f};
   if (dtype == QUIK_F16) {
     return idx_bytes == 8
-               ? dispatch_bits<__half, int64_t>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st)
-               : dispatch_bits<__half, uint16_t>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+               ? dispatch_bits<__half, int64_t, 0>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, none, st)
+               : dispatch_bits<__half, uint16_t, 0>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, none, st);
   }
   return idx_bytes == 8
-             ? dispatch_bits<__nv_bfloat16, int64_t>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st)
-             : dispatch_bits<__nv_bfloat16, uint16_t>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, st);
+             ? dispatch_bits<__nv_bfloat16, int64_t, 0>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, none, st)
+             : dispatch_bits<__nv_bfloat16, uint16_t, 0>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, none, st);
+}
+
+// The quantizer with the producer of X fused in (16-bit column ids only): prod 1 = RMSNorm with weight vector `aux` and
+// `eps`, prod 2 = SiLU(src) * aux with a second matrix `aux`.
+int launch_asym_quantize_fused(int prod, const void *src, const void *aux, float eps, int dtype, int rows, int cols,
+                               const void *int_idx, int num_int, const void *fp_idx, int num_fp, int bits, int wide,
+                               void *dst, void *meta, void *fp_x, cudaStream_t st) {
+  if (rows == 0) return QUIK_OK;
+  const RowProducer pr{aux, eps};
+  if (prod == 1) {
+    if (dtype == QUIK_F16)
+      return dispatch_bits<__half, uint16_t, 1>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
+    return dispatch_bits<__nv_bfloat16, uint16_t, 1>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
+  }
+  if (prod == 2) {
+    if (dtype == QUIK_F16)
+      return dispatch_bits<__half, uint16_t, 2>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
+    return dispatch_bits<__nv_bfloat16, uint16_t, 2>(bits, wide, src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
+  }
+  return QUIK_ERR_UNSUPPORTED;
 }
 
 int launch_find_meta(const void *src, int dtype, int rows, int cols, int bits, void *meta,

@@ -57,7 +57,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 // Bounded wait.  Returns false when the CTA is aborting (this or another wait ran out); the first wait
 // that runs out raises the CTA's abort flag and sets bit 0 of the device status word.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          unsigned int *status_word) {
+                                          unsigned int *status_word, unsigned long long limit_ns = WAIT_LIMIT_NS) {
   uint32_t spins = 0;
   unsigned long long t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
@@ -66,7 +66,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       const unsigned long long now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > WAIT_LIMIT_NS) {
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         atomicOr(status_word, 1u);
         return false;

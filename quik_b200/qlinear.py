@@ -142,6 +142,43 @@ class MixedQLinear(torch.nn.Module):
             return self.int_weight
         return self._cached("w8", self.int_weight, matmul.unpack_int4)
 
+    def _operand_layouts(self, M):
+        """(token codes packed?, weight codes packed?) for M tokens: which engine the fused launch will use."""
+        small_m_mode = _lib.config_get(_lib.CFG_SMALL_M)
+        row_ok = self.bits == 8 or self.int_features_num % 32 == 0
+        stream = M <= _lib.STREAM_M_MAX and small_m_mode != _lib.SMALL_M_OFF and row_ok
+        if self.bits == 8:
+            return False, False
+        if stream:
+            return (M <= _lib.SMALL_M_MAX and small_m_mode != _lib.SMALL_M_TCGEN05), True
+        return (row_ok and _lib.config_get(_lib.CFG_GEMM_ENGINE) == _lib.ENGINE_TCGEN05_TS), False
+
+    def _fill_shared(self, quantized, wide):
+        shared_input = self.shared_input
+        if shared_input is None:
+            raise RuntimeError("a fused producer needs a SharedQuantizedInput on the layer (group size >= 1)")
+        shared_input.qint_x, shared_input.meta, shared_input.fp_x = quantized
+        shared_input.wide = wide
+
+    def quantize_rmsnorm(self, x, norm_weight, eps):
+        """Quantizes RMSNorm(x) * norm_weight straight into this layer's shared input (one pass over x, the normalised
+        activations never go to HBM).  The following forward calls of the group's members find the codes and skip their
+        own quantizer; pass them any tensor of x's shape, dtype and device (it is not read)."""
+        x2 = x[0] if x.dim() == 3 else x
+        q_packed, _ = self._operand_layouts(x2.shape[0])
+        i16, f16 = self._idx16()
+        self._fill_shared(asymmetric.rmsnorm_quantize_u16(x2.contiguous(), norm_weight, eps, i16, f16, self.bits,
+                                                          not q_packed), not q_packed)
+
+    def quantize_silu_mul(self, gate, up):
+        """Quantizes SiLU(gate) * up straight into this layer's shared input (see :meth:`quantize_rmsnorm`)."""
+        g2 = gate[0] if gate.dim() == 3 else gate
+        u2 = up[0] if up.dim() == 3 else up
+        q_packed, _ = self._operand_layouts(g2.shape[0])
+        i16, f16 = self._idx16()
+        self._fill_shared(asymmetric.silu_mul_quantize_u16(g2.contiguous(), u2.contiguous(), i16, f16, self.bits,
+                                                           not q_packed), not q_packed)
+
     # ------------------------------------------------------------------ forward
     def forward(self, x):
         if self.int_features_num <= 0:
@@ -168,17 +205,7 @@ class MixedQLinear(torch.nn.Module):
         #     byte too, except when the engine with the token operand in tensor memory is selected: it takes 4-bit
         #     token codes packed (the reference layout) and widens them on chip.
         # (a packed 4-bit row must be a multiple of 16 bytes for these engines; otherwise both operands one per byte)
-        small_m_mode = _lib.config_get(_lib.CFG_SMALL_M)
-        row_ok = self.bits == 8 or self.int_features_num % 32 == 0
-        stream = M <= _lib.STREAM_M_MAX and small_m_mode != _lib.SMALL_M_OFF and row_ok
-        if self.bits == 8:
-            q_packed = w_packed = False
-        elif stream:
-            q_packed = M <= _lib.SMALL_M_MAX and small_m_mode != _lib.SMALL_M_TCGEN05
-            w_packed = True
-        else:
-            q_packed = row_ok and _lib.config_get(_lib.CFG_GEMM_ENGINE) == _lib.ENGINE_TCGEN05_TS
-            w_packed = False
+        q_packed, w_packed = self._operand_layouts(M)
         wide = not q_packed
         if shared_input.qint_x is not None and self.bits == 4 and shared_input.wide != wide:
             raise RuntimeError("MixedQLinear: the shared quantized input was written in another code layout than this "

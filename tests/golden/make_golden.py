@@ -94,4 +94,8 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ref_dir = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("QUIK_REFERENCE_DIR")
+    if not ref_dir:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path of the reference checkout> "
+                         "(or set QUIK_REFERENCE_DIR)")
+    main(ref_dir)

@@ -103,7 +103,7 @@ def test_two_issuing_threads_give_the_exact_product(M, N, K, tile, pair, issuers
         _lib.set_engine(_lib.ENGINE_AUTO)
         _lib.set_tile_n(0)
         _lib.set_cta_pair(0)
-        _lib.set_mma_issuers(2)
+        _lib.set_mma_issuers(1)
     assert_device_clean()
 
 
