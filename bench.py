@@ -294,12 +294,15 @@ class Workload:
                 self.sets.append([copy.deepcopy(layer) for layer in self.layers])
         self.graph = None
         self._turn = 0
+        # tensor parallel: a graph holds an even number of steps (the assembled results alternate between two
+        # buffers); inside it the assembly of a step overlaps the kernels of the following steps
+        self.graph_steps = 4 if world > 1 else len(self.sets)
 
-    def step(self):
+    def step(self, wait=True):
         layers = self.sets[self._turn % len(self.sets)]
         self._turn += 1
         outs = [layer(c.x.unsqueeze(0)) for c, layer in zip(self.cases, layers)]
-        if self.world > 1:
+        if self.world > 1 and wait:
             for layer in layers:
                 layer.wait()          # the assembled outputs are part of the step
         return outs
@@ -318,7 +321,8 @@ class Workload:
             self._turn = 0
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                self.graph_outs = [self.step() for _ in self.sets]
+                # only the last step joins the assembly streams: every output is complete when the graph ends
+                self.graph_outs = [self.step(wait=(i == self.graph_steps - 1)) for i in range(self.graph_steps)]
             self.graph = g
             for _ in range(3):
                 g.replay()
@@ -331,7 +335,7 @@ class Workload:
 
     @property
     def steps_per_run(self):
-        return len(self.sets) if self.graph is not None else 1
+        return self.graph_steps if self.graph is not None else 1
 
     def run(self):
         if self.graph is not None:

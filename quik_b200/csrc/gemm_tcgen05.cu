@@ -411,22 +411,21 @@ int launch_t(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tf
 }
 
 // ---- tile shape per problem -------------------------------------------------------------------
-// A launch is a number of waves of equally sized tiles over the resident units (CTAs or CTA pairs).  The time
-// of a tile is set by the slower of the tensor pipe (2 * block_n cycles per CTA and 128-byte k-block) and the
-// operand feed ((128 + block_n / ctas) rows of 128 bytes per CTA and k-block at kFeedBytesPerClk), so the
-// widest pair tile is the cheapest per multiply-accumulate, but a last wave that is mostly empty can cost more
-// than narrower tiles that fill their waves.  The model picks the (pair or single, block_n) with the smallest
-// waves x tile time; kFeedBytesPerClk and kTileFixedClk are fitted to measured sweeps over the Llama-2 shapes.
-constexpr double kFeedBytesPerClk = 43.0;
+// A launch is a number of waves of equally sized tiles over the resident units (CTAs or CTA pairs).  Measured on the
+// Llama-2 shapes (7B at 2048 tokens, 70B at 4096, and their column shards for 2/4/8 GPUs): the time of a tile hardly
+// depends on its width -- a tcgen05.mma with both operands in shared memory occupies its issuing thread ~217 cycles
+// whatever its N -- so per k-block a tile costs about kBlockClk + kColClk * block_n cycles.  A narrower tile is
+// therefore almost as expensive as the widest one and only pays where it saves a whole wave; among widths with the
+// same number of waves the narrowest wins by a little.
+constexpr double kBlockClk = 366.0;
+constexpr double kColClk = 0.45;
 constexpr double kTileFixedClk = 1500.0;
 
 double tile_cost(int M, int N, int kblocks, int ctas, int bn, int units) {
   const int tile_m = BLOCK_M * ctas;
   const long long tiles = (long long)((M + tile_m - 1) / tile_m) * ((N + bn - 1) / bn);
   const long long waves = (tiles + units - 1) / units;
-  const double mma = 2.0 * bn;
-  const double feed = (BLOCK_M + bn / ctas) * (double)STAGE_K_BYTES / kFeedBytesPerClk;
-  return (double)waves * (kblocks * (mma > feed ? mma : feed) + kTileFixedClk);
+  return (double)waves * (kblocks * (kBlockClk + kColClk * bn) + kTileFixedClk);
 }
 
 }  // namespace

@@ -12,8 +12,12 @@ Two ways to assemble:
 symmetric memory and the rank's fused kernel writes its own column range into it in place (output
 row pitch N).  After a stream-ordered barrier each rank pulls the g-1 remote column ranges from the
 peers' buffers into the same ranges of its own with strided copies on the copy engines
-(``quik_copy_2d``) on a side stream.  No SM time, no staging buffer, no permute pass, no local copy,
-and the transfer of layer i overlaps the kernels of layer i+1.
+(``quik_copy_2d``), one stream per peer so that several copy engines work at once.  No SM time, no
+staging buffer, no permute pass, no local copy, and the transfer of layer i overlaps the kernels of
+the layers after it.  The result alternates between two symmetric buffers, which makes one barrier
+per forward enough: a rank overwrites its column range of a buffer two forwards later, after it has
+passed the barrier of the forward in between -- and a peer reaches that barrier only when its pulls
+of the earlier forward are complete.
 
 ``mode="nccl"``: ``all_gather_into_tensor`` of the slabs followed by a permute to row-major (also
 the path used on CPU/gloo in the tests).
@@ -49,10 +53,13 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
         self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
         self.mode = mode
         self.comm_stream = comm_stream
-        self._slab = None          # symmetric [M, N/g]
-        self._hdl = None
-        self._full = None          # local [M, N]
+        self._bufs = []            # two symmetric [M, N] results, used in turn
+        self._hdls = []
+        self._turn = 0
+        self._peer_streams = []
+        self._passed = None        # event: the barrier of the last forward has been passed on the comm stream
         self._done = None          # event: assembly of the last forward finished
+        self._last = None          # result tensor of the last forward
 
     # ---- pull mode ---------------------------------------------------------------------------
     def _setup_pull(self, m, n_local, dtype, device):
@@ -60,47 +67,70 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
         n = n_local * self.world
         # the whole [M, N] result lives in symmetric memory; the local fused kernel writes its column
         # range in place (row pitch N), the peers read that range from here
-        self._full = symm_mem.empty((m, n), dtype=dtype, device=device)
-        self._hdl = symm_mem.rendezvous(self._full, self.group)
-        self._slab = self._full[:, self.rank * n_local:(self.rank + 1) * n_local]
-        self.local.out_buffer = self._slab
+        self._bufs, self._hdls = [], []
+        for _ in range(2):
+            full = symm_mem.empty((m, n), dtype=dtype, device=device)
+            self._hdls.append(symm_mem.rendezvous(full, self.group))
+            self._bufs.append(full)
+        self._turn = 0
         if self.comm_stream is None:
             self.comm_stream = torch.cuda.Stream(device=device)
+        self._peer_streams = [torch.cuda.Stream(device=device) for _ in range(self.world - 1)]
 
     def _forward_pull(self, x):
         from ._lib import check, load
         m = x.shape[-2]
         n_local = self.local.out_features
-        if self._full is None or self._full.shape[0] != m:
+        if not self._bufs or self._bufs[0].shape[0] != m:
             self._setup_pull(m, n_local, x.dtype, x.device)
+        b = self._turn & 1
+        self._turn += 1
+        full, hdl = self._bufs[b], self._hdls[b]
+        slab = full[:, self.rank * n_local:(self.rank + 1) * n_local]
+        self.local.out_buffer = slab
         cur = torch.cuda.current_stream(x.device)
-        if self._done is not None:
-            cur.wait_event(self._done)          # peers have finished reading the previous contents
-        out = self.local(x)                      # writes its column range of self._full
-        assert out.data_ptr() == self._slab.data_ptr(), "local layer did not write into the symmetric buffer"
+        if self._passed is not None:
+            # this buffer was last used two forwards ago; every peer finished pulling from it before it arrived at
+            # the barrier of the forward in between, which this rank has passed once this event has fired
+            cur.wait_event(self._passed)
+        out = self.local(x)                      # writes its column range of `full`
+        assert out.data_ptr() == slab.data_ptr(), "local layer did not write into the symmetric buffer"
         ready = torch.cuda.Event()
         ready.record(cur)
         lib = load()
-        es = self._full.element_size()
+        es = full.element_size()
         width = n_local * es
-        pitch = self._full.shape[1] * es
-        with torch.cuda.stream(self.comm_stream):
-            self.comm_stream.wait_event(ready)
-            self._hdl.barrier(channel=0)         # every rank's column range of this layer is complete
+        pitch = full.shape[1] * es
+        comm = self.comm_stream
+        with torch.cuda.stream(comm):
+            comm.wait_event(ready)
+            hdl.barrier(channel=0)               # every rank's column range of this forward is complete
+            passed = torch.cuda.Event()
+            passed.record(comm)
+            joins = []
             for step in range(1, self.world):
                 peer = (self.rank + step) % self.world      # walk the ring so the links load evenly
-                src = self._hdl.get_buffer(peer, tuple(self._full.shape), self._full.dtype)
+                src = hdl.get_buffer(peer, tuple(full.shape), full.dtype)
                 off = peer * width
-                check(lib.quik_copy_2d(self._full.data_ptr() + off, pitch, src.data_ptr() + off, pitch, width, m,
-                                       self.comm_stream.cuda_stream), "quik_copy_2d")
-            self._hdl.barrier(channel=1)         # nobody still reads a range when it is overwritten next time
+                ps = self._peer_streams[step - 1]
+                ps.wait_event(passed)
+                check(lib.quik_copy_2d(full.data_ptr() + off, pitch, src.data_ptr() + off, pitch, width, m,
+                                       ps.cuda_stream), "quik_copy_2d")
+                ev = torch.cuda.Event()
+                ev.record(ps)
+                joins.append(ev)
+            for ev in joins:
+                comm.wait_event(ev)              # the comm stream reaches its next barrier only after these pulls
+            self._passed = passed
             self._done = torch.cuda.Event()
-            self._done.record(self.comm_stream)
-        return self._full.unsqueeze(0)
+            self._done.record(comm)
+        self._last = full
+        return full.unsqueeze(0)
 
     def reset(self):
-        """Forget the completion event of earlier forwards (call before capturing a CUDA graph)."""
+        """Forget the events of earlier forwards (call before capturing a CUDA graph, with the device idle)."""
         self._done = None
+        self._passed = None
 
     def wait(self):
         """Make the current stream wait for the assembly of the last forward."""

@@ -27,12 +27,37 @@ def _worker(rank, world, port, q):
         for mode in ("nccl", "pull"):
             shard = make_layer("s", M, K, N, 4, F=64, seed=3, device=dev, clip=False, n_slice=shard_range(N, world, rank))
             layer = ColumnParallelMixedQLinear(shard.module, mode=mode)
-            for _ in range(3):                      # repeated calls reuse the slab
-                got = layer(shard.x.unsqueeze(0))
+            ok = True
+            for i in range(5):                      # repeated calls alternate between the two result buffers
+                xi = (full.x * (1.0 + 0.25 * i)).contiguous()
+                want_i = want if i == 0 else full.module(xi.unsqueeze(0))
+                got = layer(xi.unsqueeze(0))
                 if mode == "pull":
                     layer.wait()
                 torch.cuda.synchronize()
-            res[mode] = bool(torch.equal(got, want))
+                ok = ok and bool(torch.equal(got, want_i))
+            if mode == "pull":
+                # the same as a CUDA graph of four forwards (an even number keeps the buffer alternation across
+                # replays), replayed three times without host work in between
+                layer.reset()
+                torch.cuda.synchronize()
+                dist.barrier()
+                xs = [(full.x * (1.0 + 0.5 * i)).contiguous() for i in range(4)]
+                wants = [full.module(x.unsqueeze(0)).clone() for x in xs]
+                g = torch.cuda.CUDAGraph()
+                outs = []
+                with torch.cuda.graph(g):
+                    for i, x in enumerate(xs):
+                        o = layer(x.unsqueeze(0))
+                        if i >= 2:
+                            layer.wait()
+                            outs.append(o.clone())         # forwards 2 and 3 own the two buffers at the end
+                    layer.wait()
+                for _ in range(3):
+                    g.replay()
+                torch.cuda.synchronize()
+                ok = ok and bool(torch.equal(outs[0], wants[2])) and bool(torch.equal(outs[1], wants[3]))
+            res[mode] = ok
         q.put((rank, res))
     finally:
         dist.destroy_process_group()
