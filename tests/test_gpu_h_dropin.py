@@ -36,8 +36,9 @@ def ref_qlinear():
 
 def _float_layer(K, N, F, bits, seed, bias):
     g = torch.Generator().manual_seed(seed)
+    # the outlier columns depend on (seed, K) only, so that the members of a group agree on them
+    fp_idx = torch.sort(torch.randperm(K, generator=torch.Generator().manual_seed(seed + 1))[:F])[0] if F else None
     w = (0.02 * torch.randn(N, K, generator=g)).half().to(dev())
-    fp_idx = torch.sort(torch.randperm(K, generator=g)[:F])[0] if F else None
     mask = torch.ones(K, dtype=torch.bool)
     if F:
         mask[fp_idx] = False
@@ -48,7 +49,6 @@ def _float_layer(K, N, F, bits, seed, bias):
     lin = torch.nn.Linear(K, N, bias=bias)
     if bias:
         lin.bias.data = (0.1 * torch.randn(N, generator=g)).half()
-    x = torch.randn(1, 0, K)
     return lin, w, scales, fp_idx, g
 
 
