@@ -54,10 +54,16 @@ class SharedQuantizedInput:
             self.cur_group_elem = 0
 
 
-def _to_u16(idx: Tensor) -> Tensor:
-    """int64 column ids -> the same ids as 16-bit values (stored in an int16 tensor) on idx.device."""
-    a = idx.detach().cpu().numpy().astype(np.uint16)
-    return torch.from_numpy(a.view(np.int16).copy()).to(idx.device)
+def _to_u16(idx: Tensor, cols: int | None = None) -> Tensor:
+    """int64 column ids -> the same ids as 16-bit values (stored in an int16 tensor) on idx.device.
+
+    The kernels index the row in shared memory with these ids without a range check (like the reference's kernels,
+    src/asymmetric/asymmetric.cu:351-372), so ids outside [0, cols) are refused here, once per layer."""
+    a64 = idx.detach().cpu().numpy().astype(np.int64)
+    limit = 65536 if cols is None else cols
+    if a64.size and (a64.min() < 0 or a64.max() >= limit):
+        raise RuntimeError(f"MixedQLinear: column ids must lie in [0, {limit}), got [{a64.min()}, {a64.max()}]")
+    return torch.from_numpy(a64.astype(np.uint16).view(np.int16).copy()).to(idx.device)
 
 
 class MixedQLinear(torch.nn.Module):
@@ -134,7 +140,17 @@ class MixedQLinear(torch.nn.Module):
         return ent[1]
 
     def _idx16(self):
-        return (self._cached("int16", self.int_indices, _to_u16), self._cached("fp16", self.fp_indices, _to_u16))
+        k = self.in_features
+        i16 = self._cached("int16", self.int_indices, lambda t: _to_u16(t, k))
+        f16 = self._cached("fp16", self.fp_indices, lambda t: self._checked_fp_ids(t, k))
+        return i16, f16
+
+    def _checked_fp_ids(self, fp_idx, k):
+        # integer and outlier columns must not overlap (experiments/qlinear.py:168-169 asserts the same at construction)
+        both = torch.cat([self.int_indices.detach().cpu(), fp_idx.detach().cpu()])
+        if both.numel() != k or torch.unique(both).numel() != k:
+            raise RuntimeError("MixedQLinear: int_indices and fp_indices must together name every input column exactly once")
+        return _to_u16(fp_idx, k)
 
     def _weight_codes_int8(self):
         """Weight codes one per byte, the operand layout of the tensor-core engine."""

@@ -112,3 +112,23 @@ def test_concat_stacks_member_layers():
                                             torch.ones(8, 1), fp_indices=torch.arange(F), bits=4)
     with pytest.raises(AssertionError):
         qlinear.MixedQLinear.concat([mods[0], other])
+
+
+def test_column_ids_are_range_checked():
+    """The kernels trust their 16-bit column ids; the module refuses ids outside the row or overlapping sets."""
+    import pytest
+    from quik_b200.qlinear import MixedQLinear, _to_u16
+    assert _to_u16(torch.tensor([0, 5, 65535])).tolist() == [0, 5, -1]
+    with pytest.raises(RuntimeError):
+        _to_u16(torch.tensor([0, 4096]), 4096)
+    with pytest.raises(RuntimeError):
+        _to_u16(torch.tensor([-1, 3]), 4096)
+    m = MixedQLinear(64, 8, fp_features_num=8, bits=4)
+    m.int_indices = torch.arange(56)
+    m.fp_indices = torch.arange(56, 64)
+    m._idx16()
+    m2 = MixedQLinear(64, 8, fp_features_num=8, bits=4)
+    m2.int_indices = torch.arange(56)
+    m2.fp_indices = torch.arange(50, 58)            # overlaps the integer columns
+    with pytest.raises(RuntimeError):
+        m2._idx16()
