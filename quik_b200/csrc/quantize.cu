@@ -370,23 +370,17 @@ int launch_asym_rows_thr(const void *src, int rows, int cols, const void *int_id
 }
 
 // With fewer rows than SMs the row's latency is all there is: 512 threads per row (measured 2.6 / 3.4 us against
-// 2.9 / 4.1 us for 16 rows of 4096 / 11008 columns).  With many rows the kernel is bound by instruction issue and
-// latency (about 140 instructions per 8 values), so what matters is the number of warps an SM can hold: a thread that
-// keeps two chunks in registers needs 63 registers, one that keeps four needs 120.  The row is therefore shared by as
-// many threads as it takes to stay at two chunks per thread (256, 512 or 1024; rows beyond 16384 integer columns
-// gather their tail twice).
+// 2.9 / 4.1 us for 16 rows of 4096 / 11008 columns); with many rows 256 threads give more rows in flight per SM
+// (10.9 / 21 us against 13.9 / 25.8 us for 2048 rows).  Sharing a long row among 512 or 1024 threads so that every
+// thread keeps only two chunks in registers (63 registers instead of 120-128, twice the warps per SM) was measured
+// slower: 39 instead of 25 us for 2048 rows of 11008 columns, no gain at 8192 columns.
 template <typename T, int BITS, bool WIDE, typename IdxT, int PROD>
 int launch_asym_rows(const void *src, int rows, int cols, const void *int_idx, int num_int,
                      const void *fp_idx, int num_fp, void *dst, void *meta, void *fp_x, const RowProducer &pr,
                      cudaStream_t st) {
   if (rows <= num_sms())
     return launch_asym_rows_thr<T, BITS, WIDE, IdxT, 2 * kQuantThreads, PROD>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
-  const int chunks = (num_int + 7) >> 3;
-  if (chunks <= 2 * kQuantThreads)
-    return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 2, kQuantThreads, PROD>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
-  if (chunks <= 4 * kQuantThreads)
-    return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 2, 2 * kQuantThreads, PROD>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
-  return launch_asym_rows_nc<T, BITS, WIDE, IdxT, 2, 4 * kQuantThreads, PROD>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
+  return launch_asym_rows_thr<T, BITS, WIDE, IdxT, kQuantThreads, PROD>(src, rows, cols, int_idx, num_int, fp_idx, num_fp, dst, meta, fp_x, pr, st);
 }
 
 template <typename T, typename IdxT, int PROD>
