@@ -415,29 +415,34 @@ def _hold_queue(ms):
     torch.cuda._sleep(int(ms * 1.9e6))
 
 
-def per_launch_roofline(wl, timer, seconds, sync_all):
-    """The steps launched eagerly with events around each launch of the layer kernel, for at least `seconds`.  The
-    launches of a batch are enqueued behind a spinning kernel, so they start back to back whatever the host's speed."""
+def per_launch_roofline(wl, timer, seconds, sync_all, ms_step, world, dev):
+    """The steps launched eagerly with events around each launch of the layer kernel, for about `seconds`.  The
+    launches of a batch are enqueued behind a spinning kernel, so they start back to back whatever the host's speed.
+    Every rank runs the same number of steps (the counts derive from figures agreed on by all ranks): the steps of a
+    tensor-parallel run contain barriers among the ranks."""
+    import torch.distributed as dist
     wl.reset()
     sync_all()
     t0 = time.perf_counter()
     for _ in range(3):
         wl.step()
-    host_per_step = (time.perf_counter() - t0) / 3
+    torch.cuda.synchronize()
+    host = torch.tensor([(time.perf_counter() - t0) / 3], device=dev)
+    if world > 1:
+        dist.all_reduce(host, op=dist.ReduceOp.MAX)
+    host_per_step = host.item()
     sync_all()
     batch = max(1, min(50, int(0.02 / max(host_per_step, 1e-5))))        # steps the host enqueues in ~20 ms
+    batches = max(1, min(40, math.ceil(seconds / max(batch * ms_step * 1e-3, 1e-6))))
     timer.on = True
-    t0 = time.perf_counter()
-    n = 0
-    while n < 3 or (time.perf_counter() - t0 < seconds and n < 4000):
+    for _ in range(batches):
         _hold_queue(1.3 * batch * host_per_step * 1e3 + 1.0)
         for _ in range(batch):
             wl.step()
-        n += batch
         torch.cuda.synchronize()
     sync_all()
     timer.on = False
-    return timer.collect(), n
+    return timer.collect(), batch * batches
 
 
 def quantizer_times(wl, iters=30):
@@ -497,7 +502,7 @@ def measure_workload(args, wl, peaks, i8peaks, rank, world, dev, sync_all, sampl
     region = timed_region(wl, args.steps, min_seconds, sync_all, world, dev)
     ms_step = region["ms_per_step"]
     value = wl.total_ops / (ms_step * 1e-3) / 1e12
-    per, eager_steps = per_launch_roofline(wl, timer, min(0.5, min_seconds), sync_all)
+    per, eager_steps = per_launch_roofline(wl, timer, min(0.5, min_seconds), sync_all, ms_step, world, dev)
     MixedQLinear.launch_hook = None
 
     lib = _lib.load()
@@ -849,7 +854,9 @@ def main():
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"          # keeps NCCL's version banner off stdout: one JSON line only
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a short limit: a rank that falls out of step must end the run in minutes, not hold the GPUs
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=150))
     _lib.load()
     _lib.set_engine({"auto": _lib.ENGINE_AUTO, "tcgen05": _lib.ENGINE_TCGEN05, "mma_sync": _lib.ENGINE_MMA_SYNC}[args.engine])
     _lib.set_tile_n(args.tile_n)
