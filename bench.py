@@ -65,6 +65,7 @@ def parse_args():
     ap.add_argument("--config", default="", help="time one benchmark configuration layer by layer: 0, 1, 3, 4 or all")
     ap.add_argument("--engine", choices=["auto", "tcgen05", "mma_sync"], default="auto")
     ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--l2-hint", type=int, default=-1, help="override QUIK_CFG_L2_HINT (0 / 1)")
     ap.add_argument("--min-seconds", type=float, default=1.0, help="least device time of the timed region")
     ap.add_argument("--no-library-peak", action="store_true",
                     help="do not time the cuBLASLt int8 GEMM (keeps a profiler's launch list to this repository's kernels)")
@@ -860,6 +861,8 @@ def main():
     _lib.load()
     _lib.set_engine({"auto": _lib.ENGINE_AUTO, "tcgen05": _lib.ENGINE_TCGEN05, "mma_sync": _lib.ENGINE_MMA_SYNC}[args.engine])
     _lib.set_tile_n(args.tile_n)
+    if args.l2_hint >= 0:
+        _lib.check(_lib.load().quik_config_set(_lib.CFG_L2_HINT, args.l2_hint), "quik_config_set")
     dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16
 
     def sync_all():

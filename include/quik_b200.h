@@ -69,6 +69,9 @@ extern "C" {
  * their terms; the outlier product stays on one thread).  One thread cannot issue these instructions as fast as the
  * tensor pipe could execute them, but under the board's power limit the second thread was measured to gain 1-2 %. */
 #define QUIK_CFG_MMA_ISSUERS   6
+/* 1: the tiled tcgen05 engine loads its token operand (re-read by every column tile, small enough for L2) with an L2
+ * evict-last hint, so that data streaming through L2 meanwhile does not push it out; 0 (default): plain loads. */
+#define QUIK_CFG_L2_HINT       7
 
 const char *quik_version(void);
 const char *quik_strerror(int status);

@@ -103,6 +103,10 @@ int quik_config_set(int key, int value) {
     set_mma_issuers(value);
     return QUIK_OK;
   }
+  if (key == QUIK_CFG_L2_HINT) {
+    set_l2_hint(value);
+    return QUIK_OK;
+  }
   return QUIK_ERR_UNSUPPORTED;
 }
 
@@ -111,6 +115,7 @@ int quik_config_get(int key) {
   if (key == QUIK_CFG_PDL) return g_pdl;
   if (key == QUIK_CFG_CTA_PAIR) return get_cta_pair();
   if (key == QUIK_CFG_MMA_ISSUERS) return get_mma_issuers();
+  if (key == QUIK_CFG_L2_HINT) return get_l2_hint();
   if (key == QUIK_CFG_GEMM_ENGINE) return g_engine;
   if (key == QUIK_CFG_TILE_N) return get_tile_n();
   return QUIK_ERR_UNSUPPORTED;

@@ -120,6 +120,8 @@ int get_tile_n();
 void set_cta_pair(int mode);           // 0 = by shape, 1 = never, 2 = always
 void set_mma_issuers(int n);           // 1 or 2 threads issue the integer products of a tile (shared-memory operand engine)
 int get_mma_issuers();
+void set_l2_hint(int on);               // token-operand loads of the tiled GEMM carry an L2 evict-last hint
+int get_l2_hint();
 int get_cta_pair();
 void set_debug_counters(void *buf);    // device buffer of 16 x uint64 per CTA, or NULL
 unsigned long long *get_debug_counters();

@@ -25,6 +25,7 @@ struct GemmParams {
   int mode;                       // 0: int32 C, 1: dequantize
   int acc_shift;                  // the integer accumulator holds the product times 2^acc_shift (operands widened on chip)
   int a_slots;                    // operand slots in tensor memory (engine with the token operand in tensor memory)
+  int l2_hint;                    // token-operand loads carry an L2 evict-last hint
   int issuers;                    // threads that issue the integer products (engine with both operands in shared memory)
   int32_t *C;
   void *out;

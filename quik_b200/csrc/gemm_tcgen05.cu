@@ -45,6 +45,7 @@ constexpr int SECOND_ISSUER_WARP = 10;
 // launch reads each of them once.
 std::atomic<int> g_tile_n{0};                                 // 0 = choose by shape, else a multiple of 16 in [32, 256]
 std::atomic<int> g_cta_pair{0};                               // 0 = by shape, 1 = never, 2 = always
+std::atomic<int> g_l2_hint{0};                                // 1 = token-operand loads carry an L2 evict-last hint
 std::atomic<int> g_issuers{1};                                // threads that issue the integer products of a tile (1 or 2)
 std::atomic<unsigned long long *> g_dbg{nullptr};             // diagnostic counters (device memory), off by default
 
@@ -157,6 +158,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // The token operand A is read again by every column tile of the launch and fits in L2: its lines are marked to
+      // be evicted last, so that data streaming through L2 meanwhile (the weights, the outputs, a tensor-parallel
+      // rank's peer copies) does not push it out.
+      const uint64_t keep = l2_policy_evict_last();
+      const bool hint = p.l2_hint != 0;
       // one k-block range of one product of tile j into the ring
       auto feed = [&](int j, bool fp, int kb0, int kb1) {
         const int tile = unit + j * num_units;
@@ -171,7 +177,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             tma_load_2d<CTAS>(sa, &tmap_fa, fb, kb * 64, m0);
             tma_load_2d<CTAS>(sa + A_BYTES, &tmap_fb, fb, kb * 64, n0);
           } else {
-            tma_load_2d<CTAS>(sa, &tmap_a, fb, kb * STAGE_K_BYTES, m0);
+            if (hint) tma_load_2d_policy<CTAS>(sa, &tmap_a, fb, kb * STAGE_K_BYTES, m0, keep);
+            else tma_load_2d<CTAS>(sa, &tmap_a, fb, kb * STAGE_K_BYTES, m0);
             tma_load_2d<CTAS>(sa + A_BYTES, &tmap_b, fb, kb * STAGE_K_BYTES, n0);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -465,6 +472,8 @@ void set_tile_n(int n) { g_tile_n.store(n); }
 int get_tile_n() { return g_tile_n.load(); }
 void set_debug_counters(void *buf) { g_dbg.store(static_cast<unsigned long long *>(buf)); }
 unsigned long long *get_debug_counters() { return g_dbg.load(); }
+void set_l2_hint(int on) { g_l2_hint.store(on ? 1 : 0); }
+int get_l2_hint() { return g_l2_hint.load(); }
 void set_mma_issuers(int n) { g_issuers.store(n); }
 int get_mma_issuers() { return g_issuers.load(); }
 void set_cta_pair(int mode) { g_cta_pair.store(mode); }
@@ -510,6 +519,7 @@ int launch_gemm_tcgen05(const int8_t *A, const int8_t *B, int M, int N, int K, c
   // two issuing threads only for long sums: a thread can run at most one ring of stages ahead of the other, which must
   // stay well inside one tile for the per-tile barriers that both arrive on
   p.issuers = (g_issuers.load() >= 2 && p.int_kb >= 16) ? 2 : 1;
+  p.l2_hint = g_l2_hint.load();
 
   CUtensorMap ta, tb, tfa, tfb;
   int rc;

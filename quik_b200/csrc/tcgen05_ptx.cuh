@@ -96,6 +96,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         : "memory");
   }
 }
+// The load of tma_load_2d with an L2 eviction-priority hint (a policy word from l2_policy_evict_last() /
+// l2_policy_evict_first()).
+template <int CTAS>
+__device__ __forceinline__ void tma_load_2d_policy(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1,
+                                                   uint64_t policy) {
+  if (CTAS == 1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "l"(policy)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(map), "r"(bar & LEADER_ADDR_MASK), "r"(c0), "r"(c1), "l"(policy)
+        : "memory");
+  }
+}
 // Same load with an L2 eviction-priority hint (a policy word from l2_policy_evict_first()): for data that is read
 // once, so that it does not push out lines other kernels have prefetched.
 __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1,
@@ -108,6 +125,11 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
 __device__ __forceinline__ uint32_t cluster_ctarank() {
