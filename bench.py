@@ -75,6 +75,8 @@ def parse_args():
     ap.add_argument("--layers", default="", help="comma-separated subset of layer names")
     ap.add_argument("--no-graph", action="store_true",
                     help="time eager launches instead of replaying the step as a CUDA graph")
+    ap.add_argument("--tp-chunks", type=int, default=None,
+                    help="N > 1, pull mode: row blocks per layer forward (default: by the size of the output)")
     ap.add_argument("--tp-mode", choices=["pull", "nccl"], default="pull",
                     help="N > 1: assemble outputs by peer copies out of symmetric memory, or by NCCL all-gather")
     args = ap.parse_args()
@@ -275,7 +277,7 @@ def run_reference_arm(args, shapes, config):
 class Workload:
     """The layers of one benchmark step on this rank, and how to run them."""
 
-    def __init__(self, shapes, M, dev, dtype, world=1, rank=0, tp_mode="pull", copies=1):
+    def __init__(self, shapes, M, dev, dtype, world=1, rank=0, tp_mode="pull", copies=1, tp_chunks=None):
         from quik_b200 import workloads
         from quik_b200.tp import ColumnParallelMixedQLinear, shard_range
         self.shapes, self.M, self.world, self.dev = shapes, M, world, dev
@@ -284,7 +286,7 @@ class Workload:
             sl = shard_range(N, world, rank) if world > 1 else None
             c = workloads.make_layer(name, M, K, N, bits, seed=0, device=dev, dtype=dtype, n_slice=sl)
             self.cases.append(c)
-            self.layers.append(ColumnParallelMixedQLinear(c.module, mode=tp_mode) if world > 1 else c.module)
+            self.layers.append(ColumnParallelMixedQLinear(c.module, mode=tp_mode, chunks=tp_chunks) if world > 1 else c.module)
             torch.cuda.empty_cache()
         self.total_ops = sum(2.0 * M * N * K for (_, K, N, _) in shapes)           # whole job, all ranks
         self.alg_bytes = sum(c.algorithmic_bytes for c in self.cases)
@@ -679,6 +681,42 @@ def tp_parity(wl, shapes, M, dev, dtype, rank):
     return ok, name
 
 
+def tp_assembly_record(wl, world, dev, sync_all, ms_step, reps=5):
+    """N > 1, outside the timed region: the assembly of every layer's output alone (no layer kernels), device time,
+    max over ranks: the rate the peer copies reach against the link, and the link's lower bound for a step."""
+    import torch.distributed as dist
+    if not all(hasattr(layer, "assemble_again") and layer.mode == "pull" for layer in wl.layers):
+        return None
+    wl.reset()
+    for c, layer in zip(wl.cases, wl.layers):
+        layer(c.x.unsqueeze(0))
+        layer.wait()
+    torch.cuda.synchronize()
+    sync_all()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    pulled = 0
+    a.record()
+    for _ in range(reps):
+        pulled = 0
+        for layer in wl.layers:
+            pulled += layer.assemble_again()
+        for layer in wl.layers:
+            layer.wait()
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / reps], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    sync_all()
+    ms = t.item()
+    link = 770.0          # GB/s per direction per GPU, measured peer copy on this pool
+    return {"pulled_bytes_per_rank_per_step": pulled, "assembly_alone_ms": ms,
+            "assembly_alone_gbs_per_rank": pulled / (ms * 1e-3) / 1e9, "link_gbs_measured_peer_copy": link,
+            "link_bound_ms_per_step": pulled / (link * 1e9) * 1e3,
+            "step_ms_over_link_bound": ms_step / (pulled / (link * 1e9) * 1e3),
+            "row_blocks": {c.name: len(layer._row_blocks(c.M, layer.local.out_features * 2))
+                           for c, layer in zip(wl.cases, wl.layers)}}
+
+
 def decoder_block_record(dev):
     """BASELINE config 2: one Llama-2-7B-shaped decoder block, prefill of 2048 tokens."""
     try:
@@ -882,7 +920,7 @@ def main():
     M = args.tokens
     # few tokens: the weights of one set of 7B layers fit in L2, so the step walks over three sets
     copies = 3 if (M <= 128 and world == 1) else 1
-    wl = Workload(shapes, M, dev, dtype, world, rank, args.tp_mode, copies=copies)
+    wl = Workload(shapes, M, dev, dtype, world, rank, args.tp_mode, copies=copies, tp_chunks=args.tp_chunks)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -896,6 +934,10 @@ def main():
     if world > 1:
         ok, pname = tp_parity(wl, shapes, M, dev, dtype, rank)
         parity = {"tp_parity": ok, "tp_parity_layer": pname}
+        try:
+            parity["tp"] = tp_assembly_record(wl, world, dev, sync_all, main_rec["ms_per_step"])
+        except Exception as e:           # the record is an explanation, not the measurement
+            parity["tp"] = {"error": repr(e)[:200]}
     del wl
     torch.cuda.empty_cache()
 

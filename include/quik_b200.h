@@ -213,6 +213,15 @@ int quik_int4_matmul_fixed_scratch(const uint8_t *A, const uint8_t *B, int32_t *
 /* Widen packed int4 [rows, cols/2] to int8 [rows, cols] (layout rule of include/int4.h:78-98). */
 int quik_unpack_int4(const uint8_t *src, int8_t *dst, int rows, int cols, void *stream);
 
+/* Rotary position embedding in place on the q and k projections of a decoder block (the step between the
+ * q/k/v layers and attention; the reference leaves it to transformers' LlamaAttention, which computes
+ * x * cos + rotate_half(x) * sin elementwise — this call gives the same bits in one pass).
+ * q [tokens, q_heads*head_dim], k [tokens, k_heads*head_dim] row-major, cos_table / sin_table [tokens, head_dim/2]
+ * (the angle of position t, pair j: the two halves of a head share it), all of `dtype`; head_dim % 16 == 0;
+ * pointers 16-byte aligned. */
+int quik_rotary_inplace(void *q, void *k, const void *cos_table, const void *sin_table, int dtype, int tokens,
+                        int q_heads, int k_heads, int head_dim, void *stream);
+
 /* ==== fused GEMM + dequantize ==============================================================
  * quik.asymmetric.int4FusedDequantize / int8FusedDequantize
  * (src/asymmetric/asymmetric.cpp:46-88, src/asymmetric/fused_dequantize.cu:9-119) and, with

@@ -1,8 +1,8 @@
 """One Llama-2-style decoder block whose seven linear layers are MixedQLinear modules, wired the way the
 reference wires them (QUIK experiments/llama.py:394-440): q/k/v share one quantized input (group of 3),
 gate/up share one (group of 2), o and down quantize on their own (groups of 1); down_proj may run in 8 bits
-(``int8_down_proj``).  Rotary embedding and attention are plain torch (``F.scaled_dot_product_attention``): they are
-the callers on either side of the hot path, not part of it.  The producers of the quantizers' inputs are fused into
+(``int8_down_proj``).  Attention is plain torch (``F.scaled_dot_product_attention``) and rotary embedding one in-place pass over q and k
+(``fused_rope``, bit-identical to the torch expression): they are the callers on either side of the hot path, not part of it.  The producers of the quantizers' inputs are fused into
 the quantizer (``fused_producers``, default on): RMSNorm -> quantize for q/k/v and gate/up, SiLU(gate) * up -> quantize
 for down_proj, each one pass over its input with the normalised / activated matrix never written to HBM.  Weights are random (seeded) and
 quantized per output channel by symmetric round-to-nearest with clipping search, outlier columns are seed-chosen.
@@ -14,6 +14,7 @@ import math
 import torch
 import torch.nn.functional as F
 
+from ._lib import check, dtype_code, load, ptr, stream_of
 from .qlinear import MixedQLinear, SharedQuantizedInput
 from .workloads import rtn_clip_scales
 
@@ -21,7 +22,7 @@ from .workloads import rtn_clip_scales
 class QuikLlamaBlock(torch.nn.Module):
     def __init__(self, hidden=4096, heads=32, intermediate=11008, kv_heads=None, bits=4, down_bits=8,
                  fp_features=256, seed=0, device="cuda", dtype=torch.float16, eps=1e-5, rope_theta=10000.0,
-                 clip=True, keep_dense=False, fused_producers=True):
+                 clip=True, keep_dense=False, fused_producers=True, fused_rope=True):
         super().__init__()
         kv_heads = kv_heads or heads
         self.hidden, self.heads, self.kv_heads, self.head_dim = hidden, heads, kv_heads, hidden // heads
@@ -34,6 +35,8 @@ class QuikLlamaBlock(torch.nn.Module):
         self.o_shared = SharedQuantizedInput(1)
         self.down_shared = SharedQuantizedInput(1)
         self.fused_producers = fused_producers
+        self.fused_rope = fused_rope          # rotary embedding in one in-place pass (quik_rotary_inplace)
+        self._rope_cache = {}
         dense = {}
         # the members of a group must agree on the outlier columns (the cached quantized input is shared):
         # each member draws them from a generator seeded per group
@@ -80,16 +83,34 @@ class QuikLlamaBlock(torch.nn.Module):
         v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)
         return (v.to(x.dtype)) * weight
 
+    def _angles(self, s, device, dtype):
+        """cos / sin of the rotary angles for positions 0..s-1, [s, head_dim/2] in ``dtype`` (cached per length)."""
+        key = (s, str(device), dtype)
+        if self._rope_cache.get("key") != key:
+            inv = 1.0 / (self.rope_theta ** (torch.arange(0, self.head_dim, 2, device=device).float() / self.head_dim))
+            ang = torch.outer(torch.arange(s, device=device).float(), inv)
+            self._rope_cache = {"key": key, "cos": ang.cos().to(dtype).contiguous(),
+                                "sin": ang.sin().to(dtype).contiguous()}
+        return self._rope_cache["cos"], self._rope_cache["sin"]
+
     def _rope(self, q, k):
+        """q * cos + rotate_half(q) * sin on [b, heads, s, head_dim] views (plain torch)."""
         s = q.shape[-2]
-        inv = 1.0 / (self.rope_theta ** (torch.arange(0, self.head_dim, 2, device=q.device).float() / self.head_dim))
-        ang = torch.outer(torch.arange(s, device=q.device).float(), inv)
-        cos, sin = torch.cat([ang.cos(), ang.cos()], -1).to(q.dtype), torch.cat([ang.sin(), ang.sin()], -1).to(q.dtype)
+        c, sn = self._angles(s, q.device, q.dtype)
+        cos, sin = torch.cat([c, c], -1), torch.cat([sn, sn], -1)
 
         def rot(t):
             h = t.shape[-1] // 2
             return torch.cat([-t[..., h:], t[..., :h]], -1)
         return q * cos + rot(q) * sin, k * cos + rot(k) * sin
+
+    def _rope_inplace(self, q, k, s):
+        """The same rotation in one pass, in place on the q and k projections [s, heads*head_dim] (they are this
+        block's own fresh outputs); bit-identical to ``_rope``."""
+        c, sn = self._angles(s, q.device, q.dtype)
+        with torch.cuda.device(q.device):
+            check(load().quik_rotary_inplace(ptr(q), ptr(k), ptr(c), ptr(sn), dtype_code(q.dtype), s, self.heads,
+                                             self.kv_heads, self.head_dim, stream_of(q)), "rotary")
 
     _fused_groups = None
 
@@ -128,10 +149,15 @@ class QuikLlamaBlock(torch.nn.Module):
             k = lin("k_proj", h)
             v = lin("v_proj", h)
             q = lin("q_proj", h)
+        inplace = (self.fused_rope and linear is None and not fused and b == 1 and q.is_contiguous()
+                   and k.is_contiguous() and self.head_dim % 16 == 0)
+        if inplace:
+            self._rope_inplace(q, k, s)
         q = q.view(b, s, self.heads, self.head_dim).transpose(1, 2)
         k = k.view(b, s, self.kv_heads, self.head_dim).transpose(1, 2)
         v = v.view(b, s, self.kv_heads, self.head_dim).transpose(1, 2)
-        q, k = self._rope(q, k)
+        if not inplace:
+            q, k = self._rope(q, k)
         if self.kv_heads != self.heads:
             rep = self.heads // self.kv_heads
             k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)

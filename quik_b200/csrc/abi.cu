@@ -266,6 +266,18 @@ int quik_unpack_int4(const uint8_t *src, int8_t *dst, int rows, int cols, void *
   return launch_unpack_int4(src, dst, rows, cols, static_cast<cudaStream_t>(stream));
 }
 
+int quik_rotary_inplace(void *q, void *k, const void *cos_table, const void *sin_table, int dtype, int tokens,
+                        int q_heads, int k_heads, int head_dim, void *stream) {
+  if (tokens < 0 || q_heads < 0 || k_heads < 0 || head_dim <= 0 || head_dim % 16 != 0) return QUIK_ERR_SHAPE;
+  if (dtype != QUIK_F16 && dtype != QUIK_BF16) return QUIK_ERR_DTYPE;
+  if (tokens == 0 || q_heads + k_heads == 0) return QUIK_OK;
+  if (!cos_table || !sin_table || (q_heads && !q) || (k_heads && !k)) return QUIK_ERR_NULL;
+  if (!aligned16(cos_table) || !aligned16(sin_table) || (q_heads && !aligned16(q)) || (k_heads && !aligned16(k)))
+    return QUIK_ERR_ALIGN;
+  return launch_rotary(q, k, cos_table, sin_table, dtype, tokens, q_heads, k_heads, head_dim,
+                       static_cast<cudaStream_t>(stream));
+}
+
 // Brings packed int4 operands into the form the selected engine takes: the engine with the token operand in tensor
 // memory reads A packed and widens it on chip, so only B is widened into scratch; the others need both one per byte.
 // Returns the engine call's status.

@@ -17,7 +17,10 @@ staging buffer, no permute pass, no local copy, and the transfer of layer i over
 the layers after it.  The result alternates between two symmetric buffers, which makes one barrier
 per forward enough: a rank overwrites its column range of a buffer two forwards later, after it has
 passed the barrier of the forward in between -- and a peer reaches that barrier only when its pulls
-of the earlier forward are complete.
+of the earlier forward are complete.  A layer whose assembled output is large runs as ``chunks`` blocks
+of token rows (the layer is row-independent: per-token quantization, so the values do not change): the
+pulls of a block start while the kernels of the next block run, so most of the transfer hides behind the
+layer's own computation instead of starting after it.
 
 ``mode="nccl"``: ``all_gather_into_tensor`` of the slabs followed by a permute to row-major (also
 the path used on CPU/gloo in the tests).
@@ -43,8 +46,12 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
     been called (or the side stream has been joined by other means) -- the copies run on ``comm_stream``.
     """
 
+    # bytes a rank pulls per forward above which the layer is cut into row blocks (chunks=None)
+    CHUNK_BYTES = 48 << 20
+    MAX_CHUNKS = 4
+
     def __init__(self, local: torch.nn.Module, group=None, gather_output: bool = True, mode: str = "nccl",
-                 comm_stream=None):
+                 comm_stream=None, chunks=None):
         super().__init__()
         self.local = local
         self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
@@ -53,6 +60,7 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
         self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
         self.mode = mode
         self.comm_stream = comm_stream
+        self.chunks = chunks       # row blocks per forward in pull mode; None = by the size of the output
         self._bufs = []            # two symmetric [M, N] results, used in turn
         self._hdls = []
         self._turn = 0
@@ -78,7 +86,6 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
         self._peer_streams = [torch.cuda.Stream(device=device) for _ in range(self.world - 1)]
 
     def _forward_pull(self, x):
-        from ._lib import check, load
         m = x.shape[-2]
         n_local = self.local.out_features
         if not self._bufs or self._bufs[0].shape[0] != m:
@@ -86,35 +93,45 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
         b = self._turn & 1
         self._turn += 1
         full, hdl = self._bufs[b], self._hdls[b]
-        slab = full[:, self.rank * n_local:(self.rank + 1) * n_local]
-        self.local.out_buffer = slab
         cur = torch.cuda.current_stream(x.device)
         if self._passed is not None:
             # this buffer was last used two forwards ago; every peer finished pulling from it before it arrived at
-            # the barrier of the forward in between, which this rank has passed once this event has fired
+            # the barriers of the forward in between, which this rank has passed once this event has fired
             cur.wait_event(self._passed)
-        out = self.local(x)                      # writes its column range of `full`
-        assert out.data_ptr() == slab.data_ptr(), "local layer did not write into the symmetric buffer"
-        ready = torch.cuda.Event()
-        ready.record(cur)
+        width = n_local * full.element_size()
+        x2 = x.reshape(-1, x.shape[-1])
+        for r0, r1 in self._row_blocks(m, width):
+            slab = full[r0:r1, self.rank * n_local:(self.rank + 1) * n_local]
+            self.local.out_buffer = slab
+            out = self.local(x2[r0:r1].unsqueeze(0))     # writes its column range of these rows of `full`
+            assert out.data_ptr() == slab.data_ptr(), "local layer did not write into the symmetric buffer"
+            ready = torch.cuda.Event()
+            ready.record(cur)
+            self._assemble(full, hdl, r0, r1, n_local, ready)
+        self._last = full
+        return full.unsqueeze(0)
+
+    def _assemble(self, full, hdl, r0, r1, n_local, ready):
+        """On the comm stream: wait for `ready` (this rank's column range of rows [r0, r1) is written), meet the peers
+        at a barrier, pull their column ranges of those rows."""
+        from ._lib import check, load
         lib = load()
-        es = full.element_size()
-        width = n_local * es
-        pitch = full.shape[1] * es
+        width = n_local * full.element_size()
+        pitch = full.shape[1] * full.element_size()
         comm = self.comm_stream
         with torch.cuda.stream(comm):
             comm.wait_event(ready)
-            hdl.barrier(channel=0)               # every rank's column range of this forward is complete
+            hdl.barrier(channel=0)               # every rank's column range of these rows is complete
             passed = torch.cuda.Event()
             passed.record(comm)
             joins = []
             for step in range(1, self.world):
                 peer = (self.rank + step) % self.world      # walk the ring so the links load evenly
                 src = hdl.get_buffer(peer, tuple(full.shape), full.dtype)
-                off = peer * width
+                off = r0 * pitch + peer * width
                 ps = self._peer_streams[step - 1]
                 ps.wait_event(passed)
-                check(lib.quik_copy_2d(full.data_ptr() + off, pitch, src.data_ptr() + off, pitch, width, m,
+                check(lib.quik_copy_2d(full.data_ptr() + off, pitch, src.data_ptr() + off, pitch, width, r1 - r0,
                                        ps.cuda_stream), "quik_copy_2d")
                 ev = torch.cuda.Event()
                 ev.record(ps)
@@ -124,8 +141,30 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
             self._passed = passed
             self._done = torch.cuda.Event()
             self._done.record(comm)
-        self._last = full
-        return full.unsqueeze(0)
+
+    def assemble_again(self):
+        """Repeat the assembly of the last forward's buffer without running the layer (to time the transfer alone).
+        Returns the bytes this rank pulls."""
+        if self._last is None:
+            return 0
+        b = (self._turn - 1) & 1
+        full, hdl = self._bufs[b], self._hdls[b]
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(full.device))
+        self._assemble(full, hdl, 0, full.shape[0], self.local.out_features, ready)
+        return full.shape[0] * self.local.out_features * full.element_size() * (self.world - 1)
+
+    def _row_blocks(self, m, width_bytes):
+        """Row ranges of one forward: one block, or up to MAX_CHUNKS equal blocks of a multiple of 256 rows when the
+        bytes this rank pulls exceed CHUNK_BYTES per block."""
+        c = self.chunks
+        if c is None:
+            pulled = m * width_bytes * (self.world - 1)
+            c = max(1, min(self.MAX_CHUNKS, pulled // self.CHUNK_BYTES))
+        c = max(1, min(int(c), m // 256 if m >= 256 else 1))
+        rows = -(-m // c)
+        rows = -(-rows // 256) * 256 if c > 1 else m
+        return [(r0, min(m, r0 + rows)) for r0 in range(0, m, rows)]
 
     def reset(self):
         """Forget the events of earlier forwards (call before capturing a CUDA graph, with the device idle)."""

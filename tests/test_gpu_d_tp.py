@@ -20,13 +20,13 @@ def _worker(rank, world, port, q):
     try:
         from quik_b200.tp import ColumnParallelMixedQLinear, shard_range
         from quik_b200.workloads import make_layer
-        M, K, N = 256, 1024, 1024
+        M, K, N = 512, 1024, 1024
         full = make_layer("f", M, K, N, 4, F=64, seed=3, device=dev, clip=False)
         want = full.module(full.x.unsqueeze(0))
         res = {}
-        for mode in ("nccl", "pull"):
+        for key, mode, chunks in (("nccl", "nccl", None), ("pull", "pull", None), ("pull_blocks", "pull", 2)):
             shard = make_layer("s", M, K, N, 4, F=64, seed=3, device=dev, clip=False, n_slice=shard_range(N, world, rank))
-            layer = ColumnParallelMixedQLinear(shard.module, mode=mode)
+            layer = ColumnParallelMixedQLinear(shard.module, mode=mode, chunks=chunks)   # chunks=2: two row blocks of 256
             ok = True
             for i in range(5):                      # repeated calls alternate between the two result buffers
                 xi = (full.x * (1.0 + 0.25 * i)).contiguous()
@@ -57,7 +57,7 @@ def _worker(rank, world, port, q):
                     g.replay()
                 torch.cuda.synchronize()
                 ok = ok and bool(torch.equal(outs[0], wants[2])) and bool(torch.equal(outs[1], wants[3]))
-            res[mode] = ok
+            res[key] = ok
         q.put((rank, res))
     finally:
         dist.destroy_process_group()
@@ -77,4 +77,5 @@ def test_tensor_parallel_two_ranks():
         p.join(300)
         assert p.exitcode == 0
     results = dict(q.get(timeout=10) for _ in range(2))
-    assert results == {0: {"nccl": True, "pull": True}, 1: {"nccl": True, "pull": True}}
+    good = {"nccl": True, "pull": True, "pull_blocks": True}
+    assert results == {0: good, 1: good}

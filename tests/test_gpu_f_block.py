@@ -194,3 +194,35 @@ def test_silu_mul_quantize_matches_activation_then_quantize(dtype, M, K, F, bits
     if rows_same.any():
         assert (q1[rows_same] == q0[rows_same]).float().mean().item() > 1 - 1e-3
     assert_device_clean()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,seq", [(8, 8, 64, 33), (32, 8, 128, 257), (4, 2, 16, 5)])
+def test_rotary_inplace_is_bit_identical_to_the_torch_expression(dtype, heads, kv_heads, head_dim, seq):
+    """quik_rotary_inplace against x * cos + rotate_half(x) * sin in torch (transformers' apply_rotary_pos_emb
+    arithmetic): every product and sum rounds to the storage type in both, so the bits agree."""
+    blk = QuikLlamaBlock.__new__(QuikLlamaBlock)
+    torch.nn.Module.__init__(blk)
+    blk.heads, blk.kv_heads, blk.head_dim, blk.rope_theta, blk._rope_cache = heads, kv_heads, head_dim, 10000.0, {}
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(seq, heads * head_dim, generator=g).to(dtype).cuda()
+    k = torch.randn(seq, kv_heads * head_dim, generator=g).to(dtype).cuda()
+    qv = q.view(1, seq, heads, head_dim).transpose(1, 2)
+    kv = k.view(1, seq, kv_heads, head_dim).transpose(1, 2)
+    rq, rk = blk._rope(qv, kv)
+    want_q = rq.transpose(1, 2).reshape(seq, -1).clone()
+    want_k = rk.transpose(1, 2).reshape(seq, -1).clone()
+    blk._rope_inplace(q, k, seq)
+    torch.cuda.synchronize()
+    assert torch.equal(q, want_q)
+    assert torch.equal(k, want_k)
+
+
+def test_block_with_and_without_fused_rotary_agree_bitwise():
+    blk = QuikLlamaBlock(512, 8, 1024, seed=3)
+    x = torch.randn(1, 96, 512, generator=torch.Generator().manual_seed(1)).half().cuda()
+    a = blk(x).clone()
+    blk.fused_rope = False
+    b = blk(x)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)

@@ -132,3 +132,23 @@ def test_column_ids_are_range_checked():
     m2.fp_indices = torch.arange(50, 58)            # overlaps the integer columns
     with pytest.raises(RuntimeError):
         m2._idx16()
+
+
+def test_tp_row_blocks_cover_the_rows_once():
+    """Row blocks of a tensor-parallel forward: disjoint, in order, covering [0, m), multiples of 256 rows except
+    the last, one block for small outputs."""
+    from quik_b200.tp import ColumnParallelMixedQLinear as CP
+    lay = CP.__new__(CP)
+    lay.world, lay.chunks = 4, None
+    for m, width in [(4096, 28672), (4096, 2048), (16, 28672), (2048 + 128, 28672), (300, 1 << 20)]:
+        blocks = lay._row_blocks(m, width)
+        assert blocks[0][0] == 0 and blocks[-1][1] == m
+        assert all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
+        assert all((r1 - r0) % 256 == 0 for r0, r1 in blocks[:-1])
+        assert 1 <= len(blocks) <= CP.MAX_CHUNKS
+    assert len(lay._row_blocks(4096, 2048)) == 1                   # 25 MB pulled: one block
+    assert len(lay._row_blocks(4096, 28672)) == 4                  # 352 MB pulled
+    lay.chunks = 2
+    assert lay._row_blocks(4096, 2048) == [(0, 2048), (2048, 4096)]
+    lay.chunks = 8
+    assert len(lay._row_blocks(512, 2048)) == 2                    # never blocks of fewer than 256 rows
