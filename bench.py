@@ -75,8 +75,8 @@ def parse_args():
     ap.add_argument("--layers", default="", help="comma-separated subset of layer names")
     ap.add_argument("--no-graph", action="store_true",
                     help="time eager launches instead of replaying the step as a CUDA graph")
-    ap.add_argument("--tp-chunks", type=int, default=None,
-                    help="N > 1, pull mode: row blocks per layer forward (default: by the size of the output)")
+    ap.add_argument("--tp-chunks", type=int, default=1,
+                    help="N > 1, pull mode: row blocks per layer forward (0: by the size of the output)")
     ap.add_argument("--tp-mode", choices=["pull", "nccl"], default="pull",
                     help="N > 1: assemble outputs by peer copies out of symmetric memory, or by NCCL all-gather")
     args = ap.parse_args()
@@ -681,38 +681,105 @@ def tp_parity(wl, shapes, M, dev, dtype, rank):
     return ok, name
 
 
-def tp_assembly_record(wl, world, dev, sync_all, ms_step, reps=5):
-    """N > 1, outside the timed region: the assembly of every layer's output alone (no layer kernels), device time,
-    max over ranks: the rate the peer copies reach against the link, and the link's lower bound for a step."""
+def step_breakdown(wl, replays=200):
+    """Where a short step's time goes: the step's layer kernels alone (token codes quantized once and reused) and its
+    quantizer launches alone, each replayed from its own CUDA graph over all weight sets; microseconds per step."""
+    from quik_b200 import asymmetric
+
+    def timed(fn, steps):
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(replays):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1e3 / (replays * steps)
+
+    mods = [[getattr(layer, "local", layer) for layer in layers] for layers in wl.sets]
+    xs = [c.x for c in wl.cases]
+    saved = [[m.shared_input for m in ms] for ms in mods]
+    from quik_b200.qlinear import SharedQuantizedInput
+    try:
+        for ms in mods:
+            for m in ms:
+                m.shared_input = SharedQuantizedInput(1 << 60)        # quantized on the first call, then reused
+        layers_only = timed(lambda: [[m(x.unsqueeze(0)) for m, x in zip(ms, xs)] for ms in mods], len(mods))
+    finally:
+        for ms, sv in zip(mods, saved):
+            for m, sh in zip(ms, sv):
+                m.shared_input = sh
+    ids = [[m._idx16() for m in ms] for ms in mods]
+    wide = [[not m._operand_layouts(x.shape[0])[0] for m, x in zip(ms, xs)] for ms in mods]
+    quant_only = timed(lambda: [[asymmetric.quantize_u16(x, i[0], i[1], m.bits, w) for m, x, i, w in zip(ms, xs, ii, ww)]
+                                for ms, ii, ww in zip(mods, ids, wide)], len(mods))
+    return {"layer_kernels_alone_us_per_step": layers_only, "quantizers_alone_us_per_step": quant_only}
+
+
+def tp_assembly_record(wl, world, dev, sync_all, ms_step, replays=10):
+    """N > 1, outside the timed region: the assembly of every layer's output alone (no layer kernels) and the column
+    shards alone (no assembly), each replayed from a CUDA graph of two steps, device time, max over ranks: the rate the
+    peer copies reach against the link, the link's lower bound for a step, and the pace of the kernels by themselves."""
     import torch.distributed as dist
     if not all(hasattr(layer, "assemble_again") and layer.mode == "pull" for layer in wl.layers):
         return None
-    wl.reset()
-    for c, layer in zip(wl.cases, wl.layers):
-        layer(c.x.unsqueeze(0))
-        layer.wait()
+
+    def graph_time(fn):
+        wl.reset()
+        torch.cuda.synchronize()
+        sync_all()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(2):
+                fn()
+        for _ in range(2):
+            g.replay()
+        torch.cuda.synchronize()
+        sync_all()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(replays):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / (2 * replays)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sync_all()
+        del g
+        return t.item()
+
+    for c, layer in zip(wl.cases, wl.layers):           # two forwards: both result buffers exist and hold a result
+        for _ in range(2):
+            layer(c.x.unsqueeze(0))
+            layer.wait()
     torch.cuda.synchronize()
-    sync_all()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    pulled = 0
-    a.record()
-    for _ in range(reps):
-        pulled = 0
-        for layer in wl.layers:
-            pulled += layer.assemble_again()
+    pulled = [0]
+
+    def assemble_all():
+        pulled[0] = sum(layer.assemble_again() for layer in wl.layers)
         for layer in wl.layers:
             layer.wait()
-    b.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([a.elapsed_time(b) / reps], device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    sync_all()
-    ms = t.item()
+
+    def shards_only():
+        for c, layer in zip(wl.cases, wl.layers):
+            layer.local.out_buffer = None
+            layer.local(c.x.unsqueeze(0))
+
+    ms = graph_time(assemble_all)
+    ms_shards = graph_time(shards_only)
     link = 770.0          # GB/s per direction per GPU, measured peer copy on this pool
-    return {"pulled_bytes_per_rank_per_step": pulled, "assembly_alone_ms": ms,
-            "assembly_alone_gbs_per_rank": pulled / (ms * 1e-3) / 1e9, "link_gbs_measured_peer_copy": link,
-            "link_bound_ms_per_step": pulled / (link * 1e9) * 1e3,
-            "step_ms_over_link_bound": ms_step / (pulled / (link * 1e9) * 1e3),
+    bound = pulled[0] / (link * 1e9) * 1e3
+    return {"pulled_bytes_per_rank_per_step": pulled[0], "assembly_alone_ms": ms,
+            "assembly_alone_gbs_per_rank": pulled[0] / (ms * 1e-3) / 1e9, "link_gbs_measured_peer_copy": link,
+            "link_bound_ms_per_step": bound, "step_ms_over_link_bound": ms_step / bound,
+            "column_shards_alone_ms": ms_shards,
             "row_blocks": {c.name: len(layer._row_blocks(c.M, layer.local.out_features * 2))
                            for c, layer in zip(wl.cases, wl.layers)}}
 
@@ -920,7 +987,7 @@ def main():
     M = args.tokens
     # few tokens: the weights of one set of 7B layers fit in L2, so the step walks over three sets
     copies = 3 if (M <= 128 and world == 1) else 1
-    wl = Workload(shapes, M, dev, dtype, world, rank, args.tp_mode, copies=copies, tp_chunks=args.tp_chunks)
+    wl = Workload(shapes, M, dev, dtype, world, rank, args.tp_mode, copies=copies, tp_chunks=(args.tp_chunks or None))
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -954,6 +1021,11 @@ def main():
             wls = Workload(workloads.LLAMA2_7B, 16, dev, dtype, copies=3)
             small_m = measure_workload(sub, wls, peaks, i8peaks, rank, world, dev, sync_all, want_e2e=False, min_seconds=0.3)
             small_m["workload"] = "llama2-7b linear shapes, M=16 tokens, fp_features=256, three rotating weight sets"
+            try:
+                small_m["breakdown"] = step_breakdown(wls)
+                small_m["breakdown"]["step_us"] = small_m["ms_per_step"] * 1e3
+            except Exception as e:
+                small_m["breakdown"] = {"error": repr(e)[:200]}
             del wls
             torch.cuda.empty_cache()
         if args.dtype == "fp16":

@@ -276,6 +276,11 @@ int quik_mixed_linear(const void *q, int q_packed, const void *w, int w_packed,
 int quik_copy_2d(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows,
                  void *stream);
 
+/* The same copy as a kernel on `ctas` CTAs (0 = 32) with 16-byte accesses: width, pitches and pointers must be multiples
+ * of 16 bytes.  Peer memory is read with plain (cache-volatile) loads over NVLink. */
+int quik_copy_2d_sm(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows,
+                    int ctas, void *stream);
+
 /* quik_mixed_linear with a row pitch for `out` (in elements, >= N): the layer writes its N columns
  * into a wider row-major matrix, e.g. its column range of a tensor-parallel [M, N_total] result. */
 int quik_mixed_linear_ld(const void *q, int q_packed, const void *w, int w_packed,

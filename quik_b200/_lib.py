@@ -49,6 +49,7 @@ SIGNATURES = {
     "quik_unpack_int4": (_i, [_vp, _vp, _i, _i, _vp]),
     "quik_rotary_inplace": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "quik_copy_2d": (_i, [_vp, _sz, _vp, _sz, _sz, _sz, _vp]),
+    "quik_copy_2d_sm": (_i, [_vp, _sz, _vp, _sz, _sz, _sz, _i, _vp]),
     "quik_fused_dequantize": (_i, [_vp, _vp, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "quik_mixed_linear_ld": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_longlong, _i, _i, _i, _i, _i, _i, _vp]),
     "quik_mixed_linear": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),

@@ -16,7 +16,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libquik_b200.so")
-SOURCES = ["abi.cu", "quantize.cu", "dequantize.cu", "gemm_mma_sync.cu", "gemm_tcgen05.cu", "gemm_tcgen05_ts.cu", "smallm.cu", "stream_w.cu", "stream_w_mma.cu", "selftest.cu", "rotary.cu"]
+SOURCES = ["abi.cu", "quantize.cu", "dequantize.cu", "gemm_mma_sync.cu", "gemm_tcgen05.cu", "gemm_tcgen05_ts.cu", "smallm.cu", "stream_w.cu", "stream_w_mma.cu", "selftest.cu", "rotary.cu", "peer_copy.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

@@ -415,6 +415,16 @@ int quik_copy_2d(void *dst, size_t dst_pitch, const void *src, size_t src_pitch,
   return QUIK_OK;
 }
 
+int quik_copy_2d_sm(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows,
+                    int ctas, void *stream) {
+  if (rows == 0 || width_bytes == 0) return QUIK_OK;
+  if (!dst || !src) return QUIK_ERR_NULL;
+  if (dst_pitch < width_bytes || src_pitch < width_bytes || ctas < 0) return QUIK_ERR_SHAPE;
+  if (width_bytes % 16 != 0 || dst_pitch % 16 != 0 || src_pitch % 16 != 0 || !aligned16(dst) || !aligned16(src))
+    return QUIK_ERR_ALIGN;
+  return launch_peer_copy_2d(dst, dst_pitch, src, src_pitch, width_bytes, rows, ctas, static_cast<cudaStream_t>(stream));
+}
+
 // ---- int4 GEMM without any caller-provided or freshly allocated scratch -----------------------
 // The widened operands live in this fixed device array.  It is part of the library image: every GPU
 // that loads the library carries these bytes until the process exits.

@@ -174,6 +174,8 @@ int launch_asym_dequantize(const int32_t *x, const void *meta, const void *scale
 int launch_sym_dequantize(const void *x, int x_bits, const void *scale_row, const void *scale_col,
                           const void *y, void *out, int rows, int cols, cudaStream_t st);
 int launch_unpack_int4(const uint8_t *src, int8_t *dst, int rows, int cols, cudaStream_t st);
+int launch_peer_copy_2d(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes,
+                        size_t rows, int ctas, cudaStream_t st);
 int launch_rotary(void *q, void *k, const void *cos_t, const void *sin_t, int dtype, int tokens, int q_heads,
                   int k_heads, int head_dim, cudaStream_t st);
 int launch_bounded_wait_selftest(unsigned int limit_us, int *result, cudaStream_t st);   // selftest.cu

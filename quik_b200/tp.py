@@ -31,6 +31,9 @@ import torch
 import torch.distributed as dist
 
 
+_STREAMS = {}      # (device index, world size) -> {"comm": stream, "peers": [stream per peer]}
+
+
 def shard_range(n_total: int, world: int, rank: int, multiple: int = 8) -> slice:
     """Contiguous, equal-sized shard of the output channels (n_total must divide evenly)."""
     if n_total % (world * multiple) != 0:
@@ -46,12 +49,14 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
     been called (or the side stream has been joined by other means) -- the copies run on ``comm_stream``.
     """
 
-    # bytes a rank pulls per forward above which the layer is cut into row blocks (chunks=None)
+    # chunks=None: cut the layer into row blocks when a rank pulls more than CHUNK_BYTES per block.  Not the default:
+    # on 4 GPUs the 70B step measured 1.30 ms with whole layers, 1.37 ms with two and 1.44 ms with four blocks (smaller
+    # GEMMs lose more to their last wave than the earlier start of the pulls gains)
     CHUNK_BYTES = 48 << 20
     MAX_CHUNKS = 4
 
     def __init__(self, local: torch.nn.Module, group=None, gather_output: bool = True, mode: str = "nccl",
-                 comm_stream=None, chunks=None):
+                 comm_stream=None, chunks=1):
         super().__init__()
         self.local = local
         self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
@@ -60,7 +65,7 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
         self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
         self.mode = mode
         self.comm_stream = comm_stream
-        self.chunks = chunks       # row blocks per forward in pull mode; None = by the size of the output
+        self.chunks = chunks       # row blocks per forward in pull mode (1 = whole layer); None = by the size of the output
         self._bufs = []            # two symmetric [M, N] results, used in turn
         self._hdls = []
         self._turn = 0
@@ -81,9 +86,16 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
             self._hdls.append(symm_mem.rendezvous(full, self.group))
             self._bufs.append(full)
         self._turn = 0
+        # one assembly stream and one stream per peer for all layers of a device: the assemblies of successive layers
+        # run one after the other at the link's rate (several at once, each with its own streams, measured 410 GB/s
+        # per rank against 490-670 GB/s one at a time on 4 GPUs)
+        shared = _STREAMS.setdefault((device.index, self.world), {})
+        if not shared:
+            shared["comm"] = torch.cuda.Stream(device=device)
+            shared["peers"] = [torch.cuda.Stream(device=device) for _ in range(self.world - 1)]
         if self.comm_stream is None:
-            self.comm_stream = torch.cuda.Stream(device=device)
-        self._peer_streams = [torch.cuda.Stream(device=device) for _ in range(self.world - 1)]
+            self.comm_stream = shared["comm"]
+        self._peer_streams = shared["peers"]
 
     def _forward_pull(self, x):
         m = x.shape[-2]

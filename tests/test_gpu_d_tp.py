@@ -57,6 +57,11 @@ def _worker(rank, world, port, q):
                     g.replay()
                 torch.cuda.synchronize()
                 ok = ok and bool(torch.equal(outs[0], wants[2])) and bool(torch.equal(outs[1], wants[3]))
+                # drop every reference to this layer's symmetric buffers now: a view that lived on into the next
+                # variant's capture would free them there, which a capturing stream does not permit
+                del o, g, outs
+            del got, layer, shard
+            torch.cuda.synchronize()
             res[key] = ok
         q.put((rank, res))
     finally:
