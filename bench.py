@@ -66,6 +66,9 @@ def parse_args():
     ap.add_argument("--engine", choices=["auto", "tcgen05", "mma_sync"], default="auto")
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--l2-hint", type=int, default=-1, help="override QUIK_CFG_L2_HINT (0 / 1)")
+    ap.add_argument("--stream-preload", type=int, default=-1, help="override QUIK_CFG_STREAM_PRELOAD (0 / 1)")
+    ap.add_argument("--small-m-engine", type=int, default=-1,
+                    help="override QUIK_CFG_SMALL_M (0 off, 1 by layer size, 2 direct loads, 3 tcgen05 ring, 4 mma.sync ring)")
     ap.add_argument("--min-seconds", type=float, default=1.0, help="least device time of the timed region")
     ap.add_argument("--no-library-peak", action="store_true",
                     help="do not time the cuBLASLt int8 GEMM (keeps a profiler's launch list to this repository's kernels)")
@@ -968,6 +971,10 @@ def main():
     _lib.set_tile_n(args.tile_n)
     if args.l2_hint >= 0:
         _lib.check(_lib.load().quik_config_set(_lib.CFG_L2_HINT, args.l2_hint), "quik_config_set")
+    if args.small_m_engine >= 0:
+        _lib.check(_lib.load().quik_config_set(_lib.CFG_SMALL_M, args.small_m_engine), "quik_config_set")
+    if args.stream_preload >= 0:
+        _lib.check(_lib.load().quik_config_set(_lib.CFG_STREAM_PRELOAD, args.stream_preload), "quik_config_set")
     dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16
 
     def sync_all():
@@ -994,6 +1001,11 @@ def main():
         time.sleep(0.2)
     main_rec = measure_workload(args, wl, peaks, i8peaks, rank, world, dev, sync_all, sampler=sampler)
     clocks = sampler.stop(main_rec.pop("host_window", None)) if rank == 0 else None
+    if M <= 128 and world == 1:
+        try:
+            main_rec["breakdown"] = dict(step_breakdown(wl), step_us=main_rec["ms_per_step"] * 1e3)
+        except Exception as e:
+            main_rec["breakdown"] = {"error": repr(e)[:200]}
     if clocks and clocks.get("sm_mhz"):
         clocks["ms_per_step_x_sm_mhz"] = main_rec["ms_per_step"] * clocks["sm_mhz"]
 
@@ -1051,6 +1063,8 @@ def main():
                 "secondary_7b": secondary, "small_m": small_m, "decoder_block": block}
         if parity:
             line.update(parity)
+        if main_rec.get("breakdown"):
+            line["breakdown"] = main_rec["breakdown"]
         print(json.dumps(line), flush=True)
     if world > 1:
         # graphs that captured collectives and symmetric-memory barriers are released before the group goes down

@@ -72,6 +72,12 @@ extern "C" {
 /* 1: the tiled tcgen05 engine loads its token operand (re-read by every column tile, small enough for L2) with an L2
  * evict-last hint, so that data streaming through L2 meanwhile does not push it out; 0 (default): plain loads. */
 #define QUIK_CFG_L2_HINT       7
+/* Weight-streaming engine behind the TMA ring (few tokens).  The weights are constants of the layer, so their loads need
+ * not wait for the kernel that produces the token codes.  1 (default): the weight tiles of the first ring fill are
+ * loaded before that wait, the token tiles of the same stages after it (measured 56.8 against 58.1 us for the four
+ * Llama-2-7B layers at 16 tokens); 0: only an L2 prefetch of the first tiles precedes the wait; 2: like 1 plus an L2
+ * prefetch of the later tiles (measured slower: 60.7 us). */
+#define QUIK_CFG_STREAM_PRELOAD 8
 
 const char *quik_version(void);
 const char *quik_strerror(int status);

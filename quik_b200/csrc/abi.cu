@@ -15,6 +15,7 @@ thread_local char g_err[256] = "";
 // layers run; changing one while other threads launch gives each launch the old or the new value, never a mix.
 std::atomic<int> g_engine{QUIK_ENGINE_AUTO};
 std::atomic<int> g_small_m{1};
+std::atomic<int> g_stream_preload{1};
 std::atomic<int> g_pdl{1};
 }  // namespace
 
@@ -23,6 +24,8 @@ void set_cuda_error(cudaError_t e, const char *where) {
 }
 
 bool pdl_enabled() { return g_pdl != 0; }
+void set_stream_preload(int on) { g_stream_preload = on; }
+int get_stream_preload() { return g_stream_preload; }
 
 int num_sms() {
   static std::atomic<int> cached[kMaxDevices];
@@ -107,6 +110,11 @@ int quik_config_set(int key, int value) {
     set_l2_hint(value);
     return QUIK_OK;
   }
+  if (key == QUIK_CFG_STREAM_PRELOAD) {
+    if (value < 0 || value > 2) return QUIK_ERR_UNSUPPORTED;
+    g_stream_preload = value;
+    return QUIK_OK;
+  }
   return QUIK_ERR_UNSUPPORTED;
 }
 
@@ -116,6 +124,7 @@ int quik_config_get(int key) {
   if (key == QUIK_CFG_CTA_PAIR) return get_cta_pair();
   if (key == QUIK_CFG_MMA_ISSUERS) return get_mma_issuers();
   if (key == QUIK_CFG_L2_HINT) return get_l2_hint();
+  if (key == QUIK_CFG_STREAM_PRELOAD) return g_stream_preload;
   if (key == QUIK_CFG_GEMM_ENGINE) return g_engine;
   if (key == QUIK_CFG_TILE_N) return get_tile_n();
   return QUIK_ERR_UNSUPPORTED;

@@ -122,6 +122,8 @@ void set_mma_issuers(int n);           // 1 or 2 threads issue the integer produ
 int get_mma_issuers();
 void set_l2_hint(int on);               // token-operand loads of the tiled GEMM carry an L2 evict-last hint
 int get_l2_hint();
+void set_stream_preload(int on);        // weight-streaming engines load their first weight tiles before waiting for the predecessor
+int get_stream_preload();
 int get_cta_pair();
 void set_debug_counters(void *buf);    // device buffer of 16 x uint64 per CTA, or NULL
 unsigned long long *get_debug_counters();

@@ -43,6 +43,7 @@ struct MmaStreamParams {
   int nk, nf;                     // k-blocks (128 bytes of a W row each): integer part, outliers
   int splits;                     // CTAs that share one slab (= cluster size)
   int prefetch_blocks;            // k-blocks per CTA to prefetch into L2 before waiting for the predecessor
+  int preload;                    // 1: the weight tiles of the first ring fill are loaded before that wait too
   const void *meta, *scale_col, *w_reduced, *bias;
   void *out;
   long long ldo;
@@ -129,10 +130,25 @@ stream_w_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       prefetch_tmap(&tm_fx);
     }
   }
+  // The weights are constants of the layer: nothing the predecessor writes.  Before waiting for it (it produces the
+  // token codes) the producer thread fills the ring with the weight tiles of its first blocks and the warp asks L2
+  // for the tiles after those, so that the weight stream from HBM runs while the predecessor does; the token tiles of
+  // the same stages follow after the wait and complete the stages' byte counts.
+  const int pre = p.preload ? (nb < SM_STAGES ? nb : SM_STAGES) : 0;
+  if (threadIdx.x == 0) {
+    const uint64_t once = l2_policy_evict_first();      // the weights are read once
+    for (int i = 0; i < pre; ++i) {
+      const uint32_t fb = smem_u32(full_bar + i);
+      const uint32_t sw = smem_u32(tiles + i * SM_STAGE_BYTES);
+      mbar_expect_tx(fb, SM_STAGE_BYTES);
+      if (i < n_fp) tma_load_2d_hint(sw, &tm_fw, fb, (c0 + i) * 64, n0, once);
+      else tma_load_2d_hint(sw, &tm_w, fb, (kb_first + i - n_fp) * 128, n0, once);
+    }
+  }
   if (warp == 0) {
-    // ask L2 for this CTA's first weight tiles while the producer of the token codes may still run
-    const int npre = nb < p.prefetch_blocks ? nb : p.prefetch_blocks;
-    for (int i = lane; i < npre; i += 32) {
+    __syncwarp();
+    const int first = pre, last = nb < pre + p.prefetch_blocks ? nb : pre + p.prefetch_blocks;
+    for (int i = first + lane; i < last; i += 32) {
       if (i < n_fp) tma_prefetch_2d(&tm_fw, (c0 + i) * 64, n0);
       else tma_prefetch_2d(&tm_w, (kb_first + i - n_fp) * 128, n0);
     }
@@ -193,12 +209,23 @@ stream_w_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       }
     };
     int i = 0;
-    if (lane == 0 && nb > 0) issue(i++, 0);
+    if (lane == 0) {
+      if (pre > 0) {
+        for (; i < pre; ++i) {           // token tiles of the stages whose weight tiles are already under way
+          const uint32_t fb = smem_u32(full_bar + i);
+          const uint32_t sx = smem_u32(tiles + i * SM_STAGE_BYTES) + SM_W_BYTES;
+          if (i < n_fp) tma_load_2d<1>(sx, &tm_fx, fb, (c0 + i) * 64, 0);
+          else tma_load_2d<1>(sx, &tm_x, fb, (kb_first + i - n_fp) * 128, 0);
+        }
+      } else if (nb > 0) {
+        issue(i++, 0);
+      }
+    }
     __syncwarp();
     if (S > 1) cluster_arrive();
     if (lane == 0) {
       int stage = i % SM_STAGES;
-      uint32_t phase = 0;
+      uint32_t phase = (uint32_t)((i / SM_STAGES) & 1);
       for (; i < nb; ++i) {
         if (!mbar_wait(smem_u32(empty_bar + stage), phase ^ 1, abort_flag, p.status)) break;
         issue(i, stage);
@@ -361,7 +388,15 @@ int launch_stream_w_mma(const void *q, const void *w, int bits, int M, int N, in
   int splits = 1;
   while (splits < 4 && slabs * splits * 2 <= slots && total / (splits * 2) >= (p.nf > 2 ? p.nf : 2)) splits *= 2;
   p.splits = splits;
-  p.prefetch_blocks = SM_STAGES;   // deeper prefetch was measured slower: the requests delay the first real loads
+  p.preload = get_stream_preload();
+  // L2 prefetch before the wait.  Without preload: the first ring fill only (deeper was measured slower: the requests
+  // delay the first real loads).  With preload the real loads go first, and the prefetch covers the blocks after them
+  // up to 64 MiB over the CTAs resident at once (a 7B layer entirely; half of L2 at most).
+  {
+    const int resident = slabs * splits < slots ? slabs * splits : slots;
+    const int deep = (int)(((size_t)64 << 20) / SM_W_BYTES) / (resident > 0 ? resident : 1);
+    p.prefetch_blocks = p.preload == 2 ? (deep > SM_STAGES ? deep : SM_STAGES) : (p.preload == 1 ? 0 : SM_STAGES);
+  }
   p.meta = ep.meta;
   p.scale_col = ep.scale_col;
   p.w_reduced = ep.w_reduced;

@@ -84,3 +84,21 @@ def test_tensor_parallel_two_ranks():
     results = dict(q.get(timeout=10) for _ in range(2))
     good = {"nccl": True, "pull": True, "pull_blocks": True}
     assert results == {0: good, 1: good}
+
+
+@pytest.mark.parametrize("rows,width,ctas", [(64, 4096, 0), (333, 5120, 7), (1, 16, 1), (4096, 2048, 32)])
+def test_copy_2d_on_the_sms_copies_a_column_range(rows, width, ctas):
+    """quik_copy_2d_sm (the kernel form of the assembly copy) on local memory: the column range arrives, the
+    bytes beside it stay untouched; misaligned widths are refused."""
+    from quik_b200._lib import load
+    lib = load()
+    pitch_s, pitch_d = width * 3, width * 2
+    src = torch.randint(0, 255, (rows, pitch_s), dtype=torch.uint8, device="cuda")
+    dst = torch.full((rows, pitch_d), 7, dtype=torch.uint8, device="cuda")
+    rc = lib.quik_copy_2d_sm(dst.data_ptr() + width, pitch_d, src.data_ptr() + 2 * width, pitch_s, width, rows, ctas,
+                             torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dst[:, width:], src[:, 2 * width:])
+    assert bool((dst[:, :width] == 7).all())
+    assert lib.quik_copy_2d_sm(dst.data_ptr(), pitch_d, src.data_ptr(), pitch_s, 24, rows, 0, None) != 0
