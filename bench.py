@@ -51,6 +51,12 @@ NCU_TRAFFIC_BYTES = {
     (2048, 4096, 12288): 84.55e6, (2048, 4096, 4096): 26.88e6, (2048, 4096, 22016): 178.77e6, (2048, 11008, 4096): 84.54e6,
 }
 NCU_TRAFFIC_SOURCE = "profiles/gemm_tcgen05_llama7b_m2048.md"
+# The 70B layers at M = 4096 hold up to 1.3 GB per launch, more than a full-section capture should; one layer of them
+# was captured (o, 8192 -> 8192: 281.0 MB of DRAM traffic for 266.6 MB of algorithmic bytes) and the others are scaled
+# from it by their algorithmic bytes (operands and outputs cross HBM once in every layer: traffic grows in proportion).
+NCU_TRAFFIC_RATIO_70B = 281.0 / 266.6
+NCU_TRAFFIC_RATIO_SOURCE = ("profiles/gemm_tcgen05_llama70b_m4096.md (capture of the o layer; the other layers scaled "
+                            "by algorithmic bytes)")
 
 
 def parse_args():
@@ -533,10 +539,14 @@ def measure_workload(args, wl, peaks, i8peaks, rank, world, dev, sync_all, sampl
             traffic = sum(t) / len(t)
     kernel_alg_bytes = sum(c.M * (c.K - c.F) + c.N * (c.K - c.F) + 2 * c.F * (c.M + c.N) + 2 * c.M * c.N
                            for c in wl.cases) / len(wl.cases)
+    traffic_source = NCU_TRAFFIC_SOURCE if traffic else None
+    if traffic is None and world == 1 and M == 4096 and all(c.K >= 8192 for c in wl.cases):
+        traffic = NCU_TRAFFIC_RATIO_70B * kernel_alg_bytes
+        traffic_source = NCU_TRAFFIC_RATIO_SOURCE
     if tensor_bound:
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                     "frac": achieved / peak if peak else None, "traffic": traffic,
-                    "traffic_source": NCU_TRAFFIC_SOURCE if traffic else None,
+                    "traffic_source": traffic_source,
                     "algorithmic_bytes_per_launch": kernel_alg_bytes,
                     "kernel": "gemm_tcgen05_kernel (fused int8 GEMM + fp16 outlier GEMM + dequantize)",
                     "peak_source": f"sustained figure (the launches are timed inside a long region): {peak_src}; "

@@ -12,7 +12,8 @@ Two ways to assemble:
 symmetric memory and the rank's fused kernel writes its own column range into it in place (output
 row pitch N).  After a stream-ordered barrier each rank pulls the g-1 remote column ranges from the
 peers' buffers into the same ranges of its own with strided copies on the copy engines
-(``quik_copy_2d``), one stream per peer so that several copy engines work at once.  No SM time, no
+(``quik_copy_2d``), one stream per peer so that several copy engines work at once (the streams are shared
+by all layers of a device: the assemblies of successive layers run one after the other).  No SM time, no
 staging buffer, no permute pass, no local copy, and the transfer of layer i overlaps the kernels of
 the layers after it.  The result alternates between two symmetric buffers, which makes one barrier
 per forward enough: a rank overwrites its column range of a buffer two forwards later, after it has
