@@ -73,6 +73,7 @@ def parse_args():
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--l2-hint", type=int, default=-1, help="override QUIK_CFG_L2_HINT (0 / 1)")
     ap.add_argument("--stream-preload", type=int, default=-1, help="override QUIK_CFG_STREAM_PRELOAD (0 / 1)")
+    ap.add_argument("--stream-ring", type=int, default=-1, help="override QUIK_CFG_STREAM_RING (0 / 1 / 2)")
     ap.add_argument("--small-m-engine", type=int, default=-1,
                     help="override QUIK_CFG_SMALL_M (0 off, 1 by layer size, 2 direct loads, 3 tcgen05 ring, 4 mma.sync ring)")
     ap.add_argument("--min-seconds", type=float, default=1.0, help="least device time of the timed region")
@@ -983,6 +984,8 @@ def main():
         _lib.check(_lib.load().quik_config_set(_lib.CFG_L2_HINT, args.l2_hint), "quik_config_set")
     if args.small_m_engine >= 0:
         _lib.check(_lib.load().quik_config_set(_lib.CFG_SMALL_M, args.small_m_engine), "quik_config_set")
+    if args.stream_ring >= 0:
+        _lib.check(_lib.load().quik_config_set(_lib.CFG_STREAM_RING, args.stream_ring), "quik_config_set")
     if args.stream_preload >= 0:
         _lib.check(_lib.load().quik_config_set(_lib.CFG_STREAM_PRELOAD, args.stream_preload), "quik_config_set")
     dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16

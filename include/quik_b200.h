@@ -78,6 +78,12 @@ extern "C" {
  * Llama-2-7B layers at 16 tokens); 0: only an L2 prefetch of the first tiles precedes the wait; 2: like 1 plus an L2
  * prefetch of the later tiles (measured slower: 60.7 us). */
 #define QUIK_CFG_STREAM_PRELOAD 8
+/* Ring depth of the same engine: a CTA streams at (bytes in flight) / (loaded DRAM latency), and a grid of at most one
+ * CTA per SM would leave half of every SM's shared memory unused with the 5-stage ring that two CTAs per SM share.
+ * 2 (default): 11 stages when the grid has at most one CTA per SM, and a K split is halved when that brings the grid
+ * down to one CTA per SM; 0: 11 stages for such grids, splits unchanged; 1: always 5 stages.  Measured on the four
+ * Llama-2-7B layers at 16 tokens: 54.7 / 55.2 / 58.1 us per step for 2 / 0 / 1; no difference on the 70B layers. */
+#define QUIK_CFG_STREAM_RING   9
 
 const char *quik_version(void);
 const char *quik_strerror(int status);

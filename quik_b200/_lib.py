@@ -17,6 +17,7 @@ QUIK_OK = 0
 F16, BF16 = 0, 1
 CFG_GEMM_ENGINE, CFG_TILE_N, CFG_SMALL_M, CFG_CTA_PAIR, CFG_PDL, CFG_MMA_ISSUERS, CFG_L2_HINT = 1, 2, 3, 4, 5, 6, 7
 CFG_STREAM_PRELOAD = 8
+CFG_STREAM_RING = 9
 ENGINE_AUTO, ENGINE_TCGEN05, ENGINE_MMA_SYNC, ENGINE_TCGEN05_TS = 0, 1, 2, 3
 SMALL_M_MAX = 16       # most tokens of the mma.sync weight-streaming engines
 STREAM_M_MAX = 128     # most tokens of the tcgen05 weight-streaming engine

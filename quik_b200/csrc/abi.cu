@@ -16,6 +16,7 @@ thread_local char g_err[256] = "";
 std::atomic<int> g_engine{QUIK_ENGINE_AUTO};
 std::atomic<int> g_small_m{1};
 std::atomic<int> g_stream_preload{1};
+std::atomic<int> g_stream_ring{2};
 std::atomic<int> g_pdl{1};
 }  // namespace
 
@@ -26,6 +27,8 @@ void set_cuda_error(cudaError_t e, const char *where) {
 bool pdl_enabled() { return g_pdl != 0; }
 void set_stream_preload(int on) { g_stream_preload = on; }
 int get_stream_preload() { return g_stream_preload; }
+void set_stream_ring(int mode) { g_stream_ring = mode; }
+int get_stream_ring() { return g_stream_ring; }
 
 int num_sms() {
   static std::atomic<int> cached[kMaxDevices];
@@ -110,6 +113,11 @@ int quik_config_set(int key, int value) {
     set_l2_hint(value);
     return QUIK_OK;
   }
+  if (key == QUIK_CFG_STREAM_RING) {
+    if (value < 0 || value > 2) return QUIK_ERR_UNSUPPORTED;
+    g_stream_ring = value;
+    return QUIK_OK;
+  }
   if (key == QUIK_CFG_STREAM_PRELOAD) {
     if (value < 0 || value > 2) return QUIK_ERR_UNSUPPORTED;
     g_stream_preload = value;
@@ -125,6 +133,7 @@ int quik_config_get(int key) {
   if (key == QUIK_CFG_MMA_ISSUERS) return get_mma_issuers();
   if (key == QUIK_CFG_L2_HINT) return get_l2_hint();
   if (key == QUIK_CFG_STREAM_PRELOAD) return g_stream_preload;
+  if (key == QUIK_CFG_STREAM_RING) return g_stream_ring;
   if (key == QUIK_CFG_GEMM_ENGINE) return g_engine;
   if (key == QUIK_CFG_TILE_N) return get_tile_n();
   return QUIK_ERR_UNSUPPORTED;

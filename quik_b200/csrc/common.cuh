@@ -124,6 +124,8 @@ void set_l2_hint(int on);               // token-operand loads of the tiled GEMM
 int get_l2_hint();
 void set_stream_preload(int on);        // weight-streaming engines load their first weight tiles before waiting for the predecessor
 int get_stream_preload();
+void set_stream_ring(int mode);         // ring depth policy of the mma.sync streaming engine (QUIK_CFG_STREAM_RING)
+int get_stream_ring();
 int get_cta_pair();
 void set_debug_counters(void *buf);    // device buffer of 16 x uint64 per CTA, or NULL
 unsigned long long *get_debug_counters();

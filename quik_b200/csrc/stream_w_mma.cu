@@ -14,9 +14,10 @@
 //               of one m16n8k32.s8; the same split on the token side keeps the pairing, and the factor 256 is shifted
 //               out of the exact sum.  int8 / outliers: two chunks are the two k halves of one instruction.
 //               A warp releases a stage as soon as its operands are in registers.
-//   end         every warp adds its int32 partial sums into its CTA's shared-memory tile, the non-leading CTAs add
-//               their tiles into the leader's (red.shared::cluster; integer addition, order-free); the leader's two k-half warps combine
-//               their fp32 outlier sums in fixed order; 256 threads apply the dequantize arithmetic of
+//   end         the two k-half warps of a row group write their int32 and fp32 partial sums into separate tiles in
+//               drained stages of the ring; the non-leading CTAs add theirs into the leader's tile
+//               (red.shared::cluster; integer addition, order-free); 256 threads of the leader add the tiles (the
+//               outlier halves in fixed order), apply the dequantize arithmetic of
 //               QUIK src/asymmetric/asymmetric.cu:134-146 and store out[m, n].
 // Every mbarrier wait is bounded (device status word, see tcgen05_ptx.cuh).
 #include <cuda.h>
@@ -30,18 +31,22 @@ namespace {
 constexpr int SM_THREADS2 = 288;                    // TMA warp + 8 consumer warps
 constexpr int SM_ROWS = 128;                        // weight rows per CTA
 constexpr int SM_TOKENS = 16;
-constexpr int SM_STAGES = 5;
+constexpr int SM_STAGES = 5;                        // ring depth with two CTAs per SM
+constexpr int SM_STAGES_DEEP = 11;                  // ... with one CTA per SM (the grid has no more CTAs than SMs)
 constexpr int SM_W_BYTES = SM_ROWS * 128;
 constexpr int SM_X_BYTES = SM_TOKENS * 128;
 constexpr int SM_STAGE_BYTES = SM_W_BYTES + SM_X_BYTES;
 constexpr int SM_RED_BYTES = SM_TOKENS * SM_ROWS * 4;
 constexpr int SM_AUX_BYTES = 1024;
-constexpr size_t SM_SMEM = 1024 + (size_t)SM_STAGES * SM_STAGE_BYTES + SM_RED_BYTES + SM_AUX_BYTES;
+constexpr size_t sm_smem(int stages) { return 1024 + (size_t)stages * SM_STAGE_BYTES + SM_RED_BYTES + SM_AUX_BYTES; }
+static_assert(sm_smem(SM_STAGES_DEEP) <= 227 * 1024 && 2 * sm_smem(SM_STAGES) <= 227 * 1024, "shared-memory plan");
+static_assert(2 * SM_STAGES_DEEP * 8 + 4 <= 256, "barriers and the abort flag sit in front of the token scales");
 
 struct MmaStreamParams {
   int M, N;
   int nk, nf;                     // k-blocks (128 bytes of a W row each): integer part, outliers
   int splits;                     // CTAs that share one slab (= cluster size)
+  int stages;                     // ring depth (SM_STAGES or SM_STAGES_DEEP)
   int prefetch_blocks;            // k-blocks per CTA to prefetch into L2 before waiting for the predecessor
   int preload;                    // 1: the weight tiles of the first ring fill are loaded before that wait too
   const void *meta, *scale_col, *w_reduced, *bias;
@@ -49,6 +54,7 @@ struct MmaStreamParams {
   long long ldo;
   float shift_value;
   unsigned int *status;
+  unsigned long long *dbg;        // diagnostics (quik_debug_counters): 16 words per CTA, or nullptr
 };
 
 // four 8-row x 16-byte matrices; lanes 8i..8i+7 give the row addresses of matrix i; lane (g, t) receives word t of
@@ -92,11 +98,12 @@ stream_w_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                     const MmaStreamParams p) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
-  int *red = reinterpret_cast<int *>(tiles + SM_STAGES * SM_STAGE_BYTES);     // [token][row] int32 sums of this CTA
+  const int STAGES = p.stages;
+  int *red = reinterpret_cast<int *>(tiles + STAGES * SM_STAGE_BYTES);     // [token][row] int32 sums of this CTA
   unsigned char *aux = reinterpret_cast<unsigned char *>(red) + SM_RED_BYTES;
   uint64_t *full_bar = reinterpret_cast<uint64_t *>(aux);       // [STAGES] stage loaded
-  uint64_t *empty_bar = full_bar + SM_STAGES;                   // [STAGES] stage read by all 8 consumer warps
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(empty_bar + SM_STAGES);
+  uint64_t *empty_bar = full_bar + SM_STAGES_DEEP;                 // [STAGES] stage read by all 8 consumer warps
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(empty_bar + SM_STAGES_DEEP);
   float *s_srow = reinterpret_cast<float *>(aux + 256);         // [16] token scale
   float *s_zs = s_srow + SM_TOKENS;                             // [16] zero + shift * scale
   float *fp_part = reinterpret_cast<float *>(tiles);            // [token][row] outlier sums of the kh = 0 warps; reuses
@@ -114,9 +121,10 @@ stream_w_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const int n_fp = c0 < p.nf ? (c1 < p.nf ? c1 : p.nf) - c0 : 0;
   const int kb_first = c0 + n_fp - p.nf;
 
+  long long dbg_t[6] = {clock64(), 0, 0, 0, 0, 0};      // written out by thread 32 when diagnostics are on
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
-    for (int s = 0; s < SM_STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(full_bar + s), 1);
       mbar_init(smem_u32(empty_bar + s), 8);
     }
@@ -134,7 +142,7 @@ stream_w_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   // token codes) the producer thread fills the ring with the weight tiles of its first blocks and the warp asks L2
   // for the tiles after those, so that the weight stream from HBM runs while the predecessor does; the token tiles of
   // the same stages follow after the wait and complete the stages' byte counts.
-  const int pre = p.preload ? (nb < SM_STAGES ? nb : SM_STAGES) : 0;
+  const int pre = p.preload ? (nb < STAGES ? nb : STAGES) : 0;
   if (threadIdx.x == 0) {
     const uint64_t once = l2_policy_evict_first();      // the weights are read once
     for (int i = 0; i < pre; ++i) {
@@ -154,9 +162,19 @@ stream_w_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     }
   }
   pdl_wait();      // first global access below
+  dbg_t[1] = clock64();
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < pre; ++i) {      // token tiles of the stages whose weight tiles are already under way
+      const uint32_t fb = smem_u32(full_bar + i);
+      const uint32_t sx = smem_u32(tiles + i * SM_STAGE_BYTES) + SM_W_BYTES;
+      if (i < n_fp) tma_load_2d<1>(sx, &tm_fx, fb, (c0 + i) * 64, 0);
+      else tma_load_2d<1>(sx, &tm_x, fb, (kb_first + i - n_fp) * 128, 0);
+    }
+  }
   if (warp >= 1) {
     const int te = threadIdx.x - 32;
-    for (int i = te; i < SM_TOKENS * SM_ROWS; i += 256) red[i] = 0;
+    if (S > 1)       // only a cluster's leader receives remote sums; every CTA zeroes its tile all the same
+      for (int i = te; i < SM_TOKENS * SM_ROWS; i += 256) red[i] = 0;
     if (te < SM_TOKENS) {
       float s = 0.f, z = 0.f;
       if (te < p.M) {
@@ -208,28 +226,17 @@ stream_w_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         tma_load_2d<1>(sw + SM_W_BYTES, &tm_x, fb, kb * 128, 0);
       }
     };
-    int i = 0;
-    if (lane == 0) {
-      if (pre > 0) {
-        for (; i < pre; ++i) {           // token tiles of the stages whose weight tiles are already under way
-          const uint32_t fb = smem_u32(full_bar + i);
-          const uint32_t sx = smem_u32(tiles + i * SM_STAGE_BYTES) + SM_W_BYTES;
-          if (i < n_fp) tma_load_2d<1>(sx, &tm_fx, fb, (c0 + i) * 64, 0);
-          else tma_load_2d<1>(sx, &tm_x, fb, (kb_first + i - n_fp) * 128, 0);
-        }
-      } else if (nb > 0) {
-        issue(i++, 0);
-      }
-    }
+    int i = pre;                          // those stages are complete or under way
+    if (lane == 0 && pre == 0 && nb > 0) issue(i++, 0);
     __syncwarp();
     if (S > 1) cluster_arrive();
     if (lane == 0) {
-      int stage = i % SM_STAGES;
-      uint32_t phase = (uint32_t)((i / SM_STAGES) & 1);
+      int stage = i % STAGES;
+      uint32_t phase = (uint32_t)((i / STAGES) & 1);
       for (; i < nb; ++i) {
         if (!mbar_wait(smem_u32(empty_bar + stage), phase ^ 1, abort_flag, p.status)) break;
         issue(i, stage);
-        if (++stage == SM_STAGES) { stage = 0; phase ^= 1; }
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
   } else {
@@ -242,6 +249,7 @@ stream_w_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     uint32_t phase = 0;
     for (int i = 0; i < nb; ++i) {
       if (!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag, p.status)) break;
+      if (i == 0) dbg_t[2] = clock64();
       const uint32_t sw = smem_u32(tiles + stage * SM_STAGE_BYTES);
       uint32_t xa[4], xb[4], wv[4][4];
       ldmatrix_x4(xa, sw + SM_W_BYTES + (uint32_t)(mrow * 128) + chunk_off);            // tokens 0-7
@@ -278,27 +286,40 @@ stream_w_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             mma_s8(ci[nt], ae[j], be[j], ao[j], bo[j], we, wo);
           }
       }
-      if (++stage == SM_STAGES) { stage = 0; phase ^= 1; }
+      if (++stage == STAGES) { stage = 0; phase ^= 1; }
     }
   }
 
   // ================= reduction and epilogue =================
+  dbg_t[3] = clock64();
   __syncwarp();
   const bool ok = !*abort_flag;
   if (S > 1) cluster_wait();                    // every CTA of the cluster has started: the leader's tile is zero
   __syncthreads();                              // the ring has drained in this CTA: stage 0 may be reused
+  // Partial sums leave the registers through shared memory: the two k-half warps of a row group write their 16 x 32
+  // sums into separate tiles that reuse drained stages (row pitch 136 words: the paired 8-byte stores of a warp touch
+  // every bank once), the finishing thread of a weight row adds the two (and what other CTAs of the cluster sent).
+  constexpr int LD = SM_ROWS + 8;
+  int *sumA = reinterpret_cast<int *>(tiles + 1 * SM_STAGE_BYTES), *sumB = reinterpret_cast<int *>(tiles + 2 * SM_STAGE_BYTES);
+  float *fpA = fp_part, *fpB = reinterpret_cast<float *>(tiles + 3 * SM_STAGE_BYTES);
   if (warp >= 1 && ok) {
     const int cw = warp - 1, rg = cw & 3, kh = cw >> 2, g = lane >> 2, t = lane & 3;
+    int *dst = kh ? sumB : sumA;
+    float *fdst = kh ? fpB : fpA;
     // accumulator register r of n-tile nt: token g + 8 (r / 2), weight row 32 rg + 8 nt + 2 t + (r % 2)
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
+    for (int nt = 0; nt < 4; ++nt) {
+      const int row0 = 32 * rg + 8 * nt + 2 * t;
+      int v[4];
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int m = g + ((r >> 1) << 3), row = 32 * rg + 8 * nt + 2 * t + (r & 1);
-        const int v = BITS == 4 ? (ci[nt][r] >> 8) : ci[nt][r];      // exact: every product carried the factor 256
-        atomicAdd(red + m * SM_ROWS + row, v);        // this CTA's tile: the two k-half warps meet here
-        if (rank == 0 && kh == 0) fp_part[m * SM_ROWS + row] = cf[nt][r];
+      for (int r = 0; r < 4; ++r) v[r] = BITS == 4 ? (ci[nt][r] >> 8) : ci[nt][r];   // exact: every product carried the factor 256
+      *reinterpret_cast<int2 *>(dst + g * LD + row0) = make_int2(v[0], v[1]);
+      *reinterpret_cast<int2 *>(dst + (g + 8) * LD + row0) = make_int2(v[2], v[3]);
+      if (rank == 0 && p.nf > 0) {
+        *reinterpret_cast<float2 *>(fdst + g * LD + row0) = make_float2(cf[nt][0], cf[nt][1]);
+        *reinterpret_cast<float2 *>(fdst + (g + 8) * LD + row0) = make_float2(cf[nt][2], cf[nt][3]);
       }
+    }
   }
   __syncthreads();
   if (S > 1) {
@@ -306,26 +327,14 @@ stream_w_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const uint32_t red_base = map_to_rank(smem_u32(red), 0);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const int idx = (8 * ep_half + j) * SM_ROWS + ep_row;
-        red_add_cluster(red_base + (uint32_t)(idx * 4), red[idx]);
+        const int m = 8 * ep_half + j;
+        red_add_cluster(red_base + (uint32_t)((m * SM_ROWS + ep_row) * 4), sumA[m * LD + ep_row] + sumB[m * LD + ep_row]);
       }
     }
     cluster_arrive();
     cluster_wait();                             // all partial sums have reached the leader
   }
-  if (rank == 0 && ok) {
-    if (warp >= 5) {                            // kh = 1 warps: second half of the outlier sum, fixed order
-      const int rg = (warp - 1) & 3, g = lane >> 2, t = lane & 3;
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          const int m = g + ((r >> 1) << 3), row = 32 * rg + 8 * nt + 2 * t + (r & 1);
-          fp_part[m * SM_ROWS + row] += cf[nt][r];
-        }
-    }
-  }
-  __syncthreads();
+  dbg_t[4] = clock64();
   if (warp >= 1 && rank == 0 && ok) {
     const int n = n0 + ep_row;
     if (n < p.N) {
@@ -335,12 +344,21 @@ stream_w_mma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       for (int j = 0; j < 8; ++j) {
         const int m = 8 * ep_half + j;
         if (m < p.M) {
-          const int acc = red[m * SM_ROWS + ep_row];
-          const float add = fmaf(s_zs[m], wred, (p.nf > 0 ? fp_part[m * SM_ROWS + ep_row] : 0.f) + bias);
+          const int acc = sumA[m * LD + ep_row] + sumB[m * LD + ep_row] + (S > 1 ? red[m * SM_ROWS + ep_row] : 0);
+          // outlier sums of the two k halves in fixed order
+          const float add = fmaf(s_zs[m], wred, (p.nf > 0 ? fpA[m * LD + ep_row] + fpB[m * LD + ep_row] : 0.f) + bias);
           out[(size_t)m * p.ldo + n] = Traits<T>::from_float(fmaf((float)acc, s_srow[m] * scol, add));
         }
       }
     }
+  }
+  if (p.dbg && threadIdx.x == 32) {
+    unsigned long long *d = p.dbg + (size_t)blockIdx.x * 16;
+    dbg_t[5] = clock64();
+    for (int i = 0; i < 6; ++i) d[i] = (unsigned long long)dbg_t[i];
+    d[6] = (unsigned long long)nb;
+    d[7] = (unsigned long long)rank;
+    d[8] = global_timer_ns();
   }
   if (*abort_flag) {
     const unsigned long long t0 = global_timer_ns();
@@ -354,10 +372,10 @@ int launch_t(const CUtensorMap &tw, const CUtensorMap &tx, const CUtensorMap &tf
   auto kern = stream_w_mma_kernel<T, BITS>;
   static PerDeviceSmem state;
   {
-    const int rc = ensure_smem(state, kern, SM_SMEM);
+    const int rc = ensure_smem(state, kern, sm_smem(SM_STAGES_DEEP));      // the larger of the two ring depths
     if (rc != QUIK_OK) return rc;
   }
-  LaunchCfg lc(dim3(slabs * p.splits), dim3(SM_THREADS2), SM_SMEM, st, p.splits);
+  LaunchCfg lc(dim3(slabs * p.splits), dim3(SM_THREADS2), sm_smem(p.stages), st, p.splits);
   QUIK_CUDA_TRY(cudaLaunchKernelEx(&lc.cfg, kern, tw, tx, tfw, tfx, p));
   return check_launch("stream_w_mma_kernel");
 }
@@ -389,6 +407,12 @@ int launch_stream_w_mma(const void *q, const void *w, int bits, int M, int N, in
   int splits = 1;
   while (splits < 4 && slabs * splits * 2 <= slots && total / (splits * 2) >= (p.nf > 2 ? p.nf : 2)) splits *= 2;
   p.splits = splits;
+  // a grid of at most one CTA per SM leaves half of every SM's shared memory unused with the short ring: such layers
+  // get the deep one (bytes in flight per CTA / loaded DRAM latency is what a CTA streams at)
+  const int ring = get_stream_ring();
+  if (ring == 2 && splits > 1 && slabs * splits > num_sms() && slabs * (splits / 2) <= num_sms()) splits /= 2;
+  p.splits = splits;
+  p.stages = (ring != 1 && slabs * splits <= num_sms()) ? SM_STAGES_DEEP : SM_STAGES;
   p.preload = get_stream_preload();
   // L2 prefetch before the wait.  Without preload: the first ring fill only (deeper was measured slower: the requests
   // delay the first real loads).  With preload the real loads go first, and the prefetch covers the blocks after them
@@ -405,6 +429,7 @@ int launch_stream_w_mma(const void *q, const void *w, int bits, int M, int N, in
   p.out = ep.out;
   p.ldo = ep.ldo > 0 ? ep.ldo : N;
   p.shift_value = ep.shift_value;
+  p.dbg = get_debug_counters();
   p.status = device_status_word();
   if (p.status == nullptr) return QUIK_ERR_CUDA;
 
