@@ -110,7 +110,10 @@ int quik_selftest_bounded_wait(unsigned int limit_us, int *device_result, void *
  * non-NULL, every tcgen05 GEMM launch writes per-CTA cycle counters there: [0] MMA issue loop,
  * [1] of which waiting for a free accumulator region, [2] waiting for operands, [3] tiles of the CTA,
  * [4] epilogue waiting for an outlier product, [5] waiting for an integer product, [6] parking outlier
- * products, [7] final epilogues.  NULL switches it off (default).  No reference counterpart. */
+ * products, [7] final epilogues.  The ring streaming engine for few tokens (stream_w_mma) writes clock64 at [0] kernel
+ * entry, [1] after the wait for its predecessor, [2] first block consumed, [3] last block consumed, [4] after the
+ * reduction, [5] end, then [6] its number of k-blocks, [7] its rank in the cluster, [8] the global timer at its end.
+ * NULL switches it off (default).  No reference counterpart. */
 int quik_debug_counters(void *device_buffer);
 
 /* ==== asymmetric activation quantizer ======================================================

@@ -93,8 +93,8 @@ __device__ __forceinline__ void emit_codes(const uint32_t (&c)[4], uint32_t &w0,
 //      the MLP's `up` output beside its `gate` output), both roundings as torch's F.silu(gate) * up.
 template <typename T, int BITS, bool WIDE, typename IdxT, int NC, int NTHR, int PROD>
 // (up to four cached chunks fit 80 registers: three CTAs of 256 threads per SM, measured 33.2 against 35.5 us for
-// [4096, 8192]; six chunks would spill and measured slower under that bound)
-__global__ void __launch_bounds__(NTHR, (NTHR == 256 && NC <= 4) ? 3 : 1)
+// [4096, 8192]; six chunks would spill and measured slower under that bound, they keep two CTAs per SM = 128 registers)
+__global__ void __launch_bounds__(NTHR, NTHR == 256 ? (NC <= 4 ? 3 : 2) : 1)
 asym_quantize_row_kernel(const T *__restrict__ src, const IdxT *__restrict__ int_idx,
                          const IdxT *__restrict__ fp_idx, int rows, int cols, int num_int, int num_fp,
                          uint8_t *__restrict__ dst, T *__restrict__ meta, T *__restrict__ fp_x,
