@@ -87,6 +87,8 @@ def parse_args():
                     help="time eager launches instead of replaying the step as a CUDA graph")
     ap.add_argument("--tp-chunks", type=int, default=1,
                     help="N > 1, pull mode: row blocks per layer forward (0: by the size of the output)")
+    ap.add_argument("--tp-copy", choices=["auto", "ce", "sm"], default="auto",
+                    help="N > 1, pull mode: copy engines, the copy kernel, or the kernel for short rows only")
     ap.add_argument("--tp-mode", choices=["pull", "nccl"], default="pull",
                     help="N > 1: assemble outputs by peer copies out of symmetric memory, or by NCCL all-gather")
     args = ap.parse_args()
@@ -287,7 +289,7 @@ def run_reference_arm(args, shapes, config):
 class Workload:
     """The layers of one benchmark step on this rank, and how to run them."""
 
-    def __init__(self, shapes, M, dev, dtype, world=1, rank=0, tp_mode="pull", copies=1, tp_chunks=None):
+    def __init__(self, shapes, M, dev, dtype, world=1, rank=0, tp_mode="pull", copies=1, tp_chunks=None, tp_copy="auto"):
         from quik_b200 import workloads
         from quik_b200.tp import ColumnParallelMixedQLinear, shard_range
         self.shapes, self.M, self.world, self.dev = shapes, M, world, dev
@@ -296,7 +298,7 @@ class Workload:
             sl = shard_range(N, world, rank) if world > 1 else None
             c = workloads.make_layer(name, M, K, N, bits, seed=0, device=dev, dtype=dtype, n_slice=sl)
             self.cases.append(c)
-            self.layers.append(ColumnParallelMixedQLinear(c.module, mode=tp_mode, chunks=tp_chunks) if world > 1 else c.module)
+            self.layers.append(ColumnParallelMixedQLinear(c.module, mode=tp_mode, chunks=tp_chunks, copy=tp_copy) if world > 1 else c.module)
             torch.cuda.empty_cache()
         self.total_ops = sum(2.0 * M * N * K for (_, K, N, _) in shapes)           # whole job, all ranks
         self.alg_bytes = sum(c.algorithmic_bytes for c in self.cases)
@@ -1007,7 +1009,7 @@ def main():
     M = args.tokens
     # few tokens: the weights of one set of 7B layers fit in L2, so the step walks over three sets
     copies = 3 if (M <= 128 and world == 1) else 1
-    wl = Workload(shapes, M, dev, dtype, world, rank, args.tp_mode, copies=copies, tp_chunks=(args.tp_chunks or None))
+    wl = Workload(shapes, M, dev, dtype, world, rank, args.tp_mode, copies=copies, tp_chunks=(args.tp_chunks or None), tp_copy=args.tp_copy)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()

@@ -291,7 +291,7 @@ int quik_mixed_linear(const void *q, int q_packed, const void *w, int w_packed,
 int quik_copy_2d(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows,
                  void *stream);
 
-/* The same copy as a kernel on `ctas` CTAs (0 = 32) with 16-byte accesses: width, pitches and pointers must be multiples
+/* The same copy as a kernel on `ctas` CTAs of 128 threads (0 = 64) with 16-byte accesses: width, pitches and pointers must be multiples
  * of 16 bytes.  Peer memory is read with plain (cache-volatile) loads over NVLink. */
 int quik_copy_2d_sm(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows,
                     int ctas, void *stream);

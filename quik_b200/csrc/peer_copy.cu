@@ -1,7 +1,7 @@
 // Strided device-to-device copy on the SMs: rows x width_bytes with independent pitches, 16 bytes per access,
 // several loads in flight per thread.  Source or destination may be a peer GPU's memory mapped into this process
 // (plain loads and stores over NVLink).  The copy-engine form of the same copy is cudaMemcpy2DAsync; this kernel
-// exists because a few CTAs keep more requests in flight over NVLink than a copy engine does on short rows.
+// exists because the copy engines slow down on short rows (8 GPUs, rows of 2 KB: under 200 GB/s per rank).
 // Peer memory is read with cache-volatile loads: the same addresses are read again in later launches after the peer
 // has rewritten them.
 #include "common.cuh"
@@ -9,7 +9,9 @@
 namespace quik {
 namespace {
 
-constexpr int PC_THREADS = 512, PC_UNROLL = 8;
+// Small CTAs with few registers: they fit beside a resident CTA of the layer kernels (which leave about 6000 registers
+// of an SM free), so the copies run while those kernels do.
+constexpr int PC_THREADS = 128, PC_UNROLL = 4;
 
 __device__ __forceinline__ uint4 ld_cv(const void *p) {
   uint4 v;
@@ -17,7 +19,7 @@ __device__ __forceinline__ uint4 ld_cv(const void *p) {
   return v;
 }
 
-__global__ void __launch_bounds__(PC_THREADS)
+__global__ void __launch_bounds__(PC_THREADS, 12)
 peer_copy_2d_kernel(uint8_t *__restrict__ dst, size_t dst_pitch, const uint8_t *__restrict__ src, size_t src_pitch,
                     unsigned vec_per_row, size_t total_vec) {
   const size_t stride = (size_t)gridDim.x * PC_THREADS;
@@ -48,7 +50,7 @@ int launch_peer_copy_2d(void *dst, size_t dst_pitch, const void *src, size_t src
   const size_t vec_per_row = width_bytes / 16, total = vec_per_row * rows;
   if (total == 0) return QUIK_OK;
   size_t need = (total + PC_THREADS - 1) / PC_THREADS;
-  int grid = ctas > 0 ? ctas : 32;
+  int grid = ctas > 0 ? ctas : 64;
   if ((size_t)grid > need) grid = (int)need;
   peer_copy_2d_kernel<<<grid, PC_THREADS, 0, st>>>(static_cast<uint8_t *>(dst), dst_pitch,
                                                    static_cast<const uint8_t *>(src), src_pitch,

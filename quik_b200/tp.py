@@ -55,9 +55,14 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
     # GEMMs lose more to their last wave than the earlier start of the pulls gains)
     CHUNK_BYTES = 48 << 20
     MAX_CHUNKS = 4
+    # The copy engines slow down on short rows (8 GPUs, 70B shapes: the three layers with 2-2.5 KB per row and rank
+    # moved at under 200 GB/s per rank, the one with 14 KB rows at about 650): column ranges narrower than this many
+    # bytes are pulled by a copy kernel instead (quik_copy_2d_sm: small CTAs that fit beside the layer kernels)
+    SM_COPY_BELOW = 8192
+    SM_COPY_CTAS = 64
 
     def __init__(self, local: torch.nn.Module, group=None, gather_output: bool = True, mode: str = "nccl",
-                 comm_stream=None, chunks=1):
+                 comm_stream=None, chunks=1, copy="auto"):
         super().__init__()
         self.local = local
         self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
@@ -66,6 +71,7 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
         self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
         self.mode = mode
         self.comm_stream = comm_stream
+        self.copy = copy           # "ce": copy engines; "sm": copy kernel; "auto": the kernel for rows below SM_COPY_BELOW
         self.chunks = chunks       # row blocks per forward in pull mode (1 = whole layer); None = by the size of the output
         self._bufs = []            # two symmetric [M, N] results, used in turn
         self._hdls = []
@@ -144,8 +150,12 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
                 off = r0 * pitch + peer * width
                 ps = self._peer_streams[step - 1]
                 ps.wait_event(passed)
-                check(lib.quik_copy_2d(full.data_ptr() + off, pitch, src.data_ptr() + off, pitch, width, r1 - r0,
-                                       ps.cuda_stream), "quik_copy_2d")
+                if self.copy == "sm" or (self.copy == "auto" and width < self.SM_COPY_BELOW and width % 16 == 0):
+                    check(lib.quik_copy_2d_sm(full.data_ptr() + off, pitch, src.data_ptr() + off, pitch, width, r1 - r0,
+                                              self.SM_COPY_CTAS, ps.cuda_stream), "quik_copy_2d_sm")
+                else:
+                    check(lib.quik_copy_2d(full.data_ptr() + off, pitch, src.data_ptr() + off, pitch, width, r1 - r0,
+                                           ps.cuda_stream), "quik_copy_2d")
                 ev = torch.cuda.Event()
                 ev.record(ps)
                 joins.append(ev)

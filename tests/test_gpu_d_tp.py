@@ -24,9 +24,11 @@ def _worker(rank, world, port, q):
         full = make_layer("f", M, K, N, 4, F=64, seed=3, device=dev, clip=False)
         want = full.module(full.x.unsqueeze(0))
         res = {}
-        for key, mode, chunks in (("nccl", "nccl", None), ("pull", "pull", None), ("pull_blocks", "pull", 2)):
+        for key, mode, chunks in (("nccl", "nccl", None), ("pull", "pull", None), ("pull_blocks", "pull", 2),
+                                  ("pull_ce", "pull", None)):
             shard = make_layer("s", M, K, N, 4, F=64, seed=3, device=dev, clip=False, n_slice=shard_range(N, world, rank))
-            layer = ColumnParallelMixedQLinear(shard.module, mode=mode, chunks=chunks)   # chunks=2: two row blocks of 256
+            layer = ColumnParallelMixedQLinear(shard.module, mode=mode, chunks=chunks,      # chunks=2: two row blocks of 256
+                                               copy="ce" if key == "pull_ce" else "auto")  # auto: 1 KB rows go through the copy kernel
             ok = True
             for i in range(5):                      # repeated calls alternate between the two result buffers
                 xi = (full.x * (1.0 + 0.25 * i)).contiguous()
@@ -82,7 +84,7 @@ def test_tensor_parallel_two_ranks():
         p.join(300)
         assert p.exitcode == 0
     results = dict(q.get(timeout=10) for _ in range(2))
-    good = {"nccl": True, "pull": True, "pull_blocks": True}
+    good = {"nccl": True, "pull": True, "pull_blocks": True, "pull_ce": True}
     assert results == {0: good, 1: good}
 
 
