@@ -87,7 +87,7 @@ def parse_args():
                     help="time eager launches instead of replaying the step as a CUDA graph")
     ap.add_argument("--tp-chunks", type=int, default=1,
                     help="N > 1, pull mode: row blocks per layer forward (0: by the size of the output)")
-    ap.add_argument("--tp-copy", choices=["auto", "ce", "sm"], default="auto",
+    ap.add_argument("--tp-copy", choices=["auto", "ce", "sm"], default="ce",
                     help="N > 1, pull mode: copy engines, the copy kernel, or the kernel for short rows only")
     ap.add_argument("--tp-mode", choices=["pull", "nccl"], default="pull",
                     help="N > 1: assemble outputs by peer copies out of symmetric memory, or by NCCL all-gather")
@@ -289,7 +289,7 @@ def run_reference_arm(args, shapes, config):
 class Workload:
     """The layers of one benchmark step on this rank, and how to run them."""
 
-    def __init__(self, shapes, M, dev, dtype, world=1, rank=0, tp_mode="pull", copies=1, tp_chunks=None, tp_copy="auto"):
+    def __init__(self, shapes, M, dev, dtype, world=1, rank=0, tp_mode="pull", copies=1, tp_chunks=None, tp_copy="ce"):
         from quik_b200 import workloads
         from quik_b200.tp import ColumnParallelMixedQLinear, shard_range
         self.shapes, self.M, self.world, self.dev = shapes, M, world, dev
@@ -970,15 +970,6 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if args.config:
-        run_config_table(args, dev)
-        return
-    if world > 1:
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"          # keeps NCCL's version banner off stdout: one JSON line only
-        import datetime
-        # a short limit: a rank that falls out of step must end the run in minutes, not hold the GPUs
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=150))
     _lib.load()
     _lib.set_engine({"auto": _lib.ENGINE_AUTO, "tcgen05": _lib.ENGINE_TCGEN05, "mma_sync": _lib.ENGINE_MMA_SYNC}[args.engine])
     _lib.set_tile_n(args.tile_n)
@@ -990,6 +981,15 @@ def main():
         _lib.check(_lib.load().quik_config_set(_lib.CFG_STREAM_RING, args.stream_ring), "quik_config_set")
     if args.stream_preload >= 0:
         _lib.check(_lib.load().quik_config_set(_lib.CFG_STREAM_PRELOAD, args.stream_preload), "quik_config_set")
+    if args.config:
+        run_config_table(args, dev)
+        return
+    if world > 1:
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"          # keeps NCCL's version banner off stdout: one JSON line only
+        import datetime
+        # a short limit: a rank that falls out of step must end the run in minutes, not hold the GPUs
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=150))
     dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16
 
     def sync_all():

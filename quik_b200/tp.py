@@ -55,14 +55,15 @@ class ColumnParallelMixedQLinear(torch.nn.Module):
     # GEMMs lose more to their last wave than the earlier start of the pulls gains)
     CHUNK_BYTES = 48 << 20
     MAX_CHUNKS = 4
-    # The copy engines slow down on short rows (8 GPUs, 70B shapes: the three layers with 2-2.5 KB per row and rank
-    # moved at under 200 GB/s per rank, the one with 14 KB rows at about 650): column ranges narrower than this many
-    # bytes are pulled by a copy kernel instead (quik_copy_2d_sm: small CTAs that fit beside the layer kernels)
+    # copy="auto" pulls column ranges narrower than SM_COPY_BELOW bytes with a copy kernel (quik_copy_2d_sm: small CTAs
+    # that fit beside the layer kernels) instead of the copy engines.  Not the default: on 8 GPUs (70B shapes, 2-2.5 KB
+    # per row and rank in three of the four layers) the assembly alone went from 1.74 to 1.64 ms, but the step from 1.91
+    # to 1.99 ms (the copy CTAs take issue slots from the layer kernels); on 4 GPUs the two measured alike.
     SM_COPY_BELOW = 8192
     SM_COPY_CTAS = 64
 
     def __init__(self, local: torch.nn.Module, group=None, gather_output: bool = True, mode: str = "nccl",
-                 comm_stream=None, chunks=1, copy="auto"):
+                 comm_stream=None, chunks=1, copy="ce"):
         super().__init__()
         self.local = local
         self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)

@@ -25,10 +25,10 @@ def _worker(rank, world, port, q):
         want = full.module(full.x.unsqueeze(0))
         res = {}
         for key, mode, chunks in (("nccl", "nccl", None), ("pull", "pull", None), ("pull_blocks", "pull", 2),
-                                  ("pull_ce", "pull", None)):
+                                  ("pull_sm", "pull", None)):
             shard = make_layer("s", M, K, N, 4, F=64, seed=3, device=dev, clip=False, n_slice=shard_range(N, world, rank))
             layer = ColumnParallelMixedQLinear(shard.module, mode=mode, chunks=chunks,      # chunks=2: two row blocks of 256
-                                               copy="ce" if key == "pull_ce" else "auto")  # auto: 1 KB rows go through the copy kernel
+                                               copy="auto" if key == "pull_sm" else "ce")  # auto: these 1 KB rows go through the copy kernel
             ok = True
             for i in range(5):                      # repeated calls alternate between the two result buffers
                 xi = (full.x * (1.0 + 0.25 * i)).contiguous()
@@ -84,7 +84,7 @@ def test_tensor_parallel_two_ranks():
         p.join(300)
         assert p.exitcode == 0
     results = dict(q.get(timeout=10) for _ in range(2))
-    good = {"nccl": True, "pull": True, "pull_blocks": True, "pull_ce": True}
+    good = {"nccl": True, "pull": True, "pull_blocks": True, "pull_sm": True}
     assert results == {0: good, 1: good}
 
 
