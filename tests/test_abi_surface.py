@@ -52,6 +52,21 @@ def test_host_only_entry_points():
     assert lib.quik_int8_matmul(None, None, None, 4, 4, 24, None) == -3
     assert lib.quik_int8_matmul(None, None, None, 4, 4, 32, None) == -1
     assert lib.quik_int4_matmul(1024, 2048, 4096, 4, 4, 64, None, 0, None) == -7
+    # settings of the streaming engines: ranges checked, defaults restored
+    for key, default, bad in ((_lib.CFG_STREAM_PRELOAD, 1, 3), (_lib.CFG_STREAM_RING, 2, 3), (_lib.CFG_MMA_ISSUERS, 1, 3)):
+        assert lib.quik_config_get(key) == default
+        assert lib.quik_config_set(key, bad) != 0 and lib.quik_config_get(key) == default
+        other = 2 if key == _lib.CFG_MMA_ISSUERS else 0
+        assert lib.quik_config_set(key, other) == 0 and lib.quik_config_get(key) == other
+        assert lib.quik_config_set(key, default) == 0
+    # rotary embedding and the copy kernel: shapes and alignment are refused before any CUDA call
+    assert lib.quik_rotary_inplace(16, 16, 16, 16, 0, 4, 2, 2, 24, None) == -3          # head_dim % 16
+    assert lib.quik_rotary_inplace(16, 16, 16, 16, 9, 4, 2, 2, 32, None) == -5          # dtype code
+    assert lib.quik_rotary_inplace(None, None, None, None, 0, 0, 2, 2, 32, None) == 0   # no tokens: nothing to do
+    assert lib.quik_rotary_inplace(16, 16, 16, 24, 0, 4, 2, 2, 32, None) == -4          # table not 16-byte aligned
+    assert lib.quik_copy_2d_sm(16, 64, 32, 64, 24, 4, 0, None) == -4                    # width % 16
+    assert lib.quik_copy_2d_sm(16, 16, 32, 64, 32, 4, 0, None) == -3                    # pitch below the width
+    assert lib.quik_copy_2d_sm(None, 64, None, 64, 0, 4, 0, None) == 0                  # empty copy
 
 
 def test_python_surface_matches_reference_names():

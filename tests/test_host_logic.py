@@ -152,3 +152,14 @@ def test_tp_row_blocks_cover_the_rows_once():
     assert lay._row_blocks(4096, 2048) == [(0, 2048), (2048, 4096)]
     lay.chunks = 8
     assert len(lay._row_blocks(512, 2048)) == 2                    # never blocks of fewer than 256 rows
+
+
+def test_diagnostics_and_bench_import_without_a_gpu():
+    """The diagnostics module and bench.py import on a machine without a GPU (they fail only when asked to run)."""
+    import importlib
+    import subprocess
+    import sys
+    importlib.import_module("quik_b200.diagnostics")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--help"], capture_output=True, text=True)
+    assert r.returncode == 0 and "--tp-copy" in r.stdout and "--stream-ring" in r.stdout
